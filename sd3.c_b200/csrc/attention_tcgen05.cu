@@ -1,0 +1,368 @@
+// Flash-style attention for head_dim 64 on tcgen05 / TMEM (bf16 operands, fp32
+// softmax and accumulation, non-causal, no mask), used for the joint
+// context||image attention of every block and the image-only attention of the
+// dual blocks.
+//
+// One CTA owns a 128-query tile of one (sample, head).  Warp 0 streams K and V
+// tiles (128 keys each) with TMA from the packed (B, T, 3E) q|k|v buffer, warp
+// 1 issues S = Q K^T into TMEM, the four softmax warps (one query row per
+// thread, TMEM lane == row) turn S into P = exp2(S c - m c) in place (bf16,
+// packed two per TMEM column, aliasing the S columns), and warp 1 then issues
+// O += P V with P read from TMEM and V from shared memory in MN-major form.
+// The T x T score matrix is never written to memory.  Two CTAs are resident
+// per SM so one CTA's softmax overlaps the other's MMAs.
+//
+// Replaces mha_cuda (cuda/dit.cu:612-652: two cublasSgemmStridedBatched calls
+// around scale_softmax_kernel2, cuda/dit.cu:548-608, over materialised T x T
+// matrices) and the layout kernels fused_concat_permute /
+// fused_unpermute_split (cuda/dit.cu:475-545): the epilogue writes (B, T, E)
+// rows straight into the context and image output buffers.
+#include <cuda.h>
+
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace sd3 {
+
+int encode_tmap_3d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t d0, uint64_t d1,
+                   uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0,
+                   uint32_t box1, uint32_t box2);
+
+namespace {
+
+constexpr int AT_BM = 128;      // queries per CTA
+constexpr int AT_BN = 128;      // keys per tile
+constexpr int AT_D = 64;        // head dim
+constexpr int AT_STAGES = 2;    // K/V ring depth
+constexpr int AT_TILE_BYTES = AT_BN * AT_D * 2;  // 16 KiB
+constexpr int AT_THREADS = 192;
+constexpr int AT_TMEM_COLS = 256;
+constexpr int AT_S_COL = 0;     // S: 128 fp32 columns; P (bf16 pairs) reuses columns [0, 64)
+constexpr int AT_O_COL = 128;   // O: 64 fp32 columns
+constexpr int AT_SMEM_BYTES = (1 + 2 * AT_STAGES) * AT_TILE_BYTES + 256 + 1024;
+
+struct AttnArgs {
+  int B, T, NH, Tc, E;
+  bf16* out_c;
+  bf16* out_x;
+  float scale_log2e;
+  int* status;
+};
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(AT_THREADS, 2)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* q_smem = smem;
+  uint8_t* k_smem = smem + AT_TILE_BYTES;
+  uint8_t* v_smem = k_smem + AT_STAGES * AT_TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_smem + AT_STAGES * AT_TILE_BYTES);
+  uint64_t* q_full = bars;                  // 1
+  uint64_t* k_full = bars + 1;              // AT_STAGES
+  uint64_t* v_full = k_full + AT_STAGES;    // AT_STAGES
+  uint64_t* k_empty = v_full + AT_STAGES;   // AT_STAGES
+  uint64_t* v_empty = k_empty + AT_STAGES;  // AT_STAGES
+  uint64_t* s_full = v_empty + AT_STAGES;   // 1
+  uint64_t* p_ready = s_full + 1;           // 1
+  uint64_t* o_full = p_ready + 1;           // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+  int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q0 = blockIdx.x * AT_BM;
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int T = a.T;
+  const int nkv = (T + AT_BN - 1) / AT_BN;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < AT_STAGES; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_ready, 4);
+    mbar_init(o_full, 1);
+    *s_abort = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmQKV);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, AT_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const WaitCtx wc{s_abort, a.status};
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      mbar_expect_tx(q_full, AT_TILE_BYTES);
+      tma_load_3d(q_smem, &tmQKV, q_full, h * AT_D, q0, b);
+    }
+    __syncwarp();
+    for (int j = 0; j < nkv; ++j) {
+      const int st = j % AT_STAGES;
+      const uint32_t ph = (j / AT_STAGES) & 1;
+      if (!mbar_wait(&k_empty[st], ph ^ 1, wc, DEV_TIMEOUT_ATTN_KV)) break;
+      if (lane == 0) {
+        mbar_expect_tx(&k_full[st], AT_TILE_BYTES);
+        tma_load_3d(k_smem + st * AT_TILE_BYTES, &tmQKV, &k_full[st], a.E + h * AT_D, j * AT_BN, b);
+      }
+      __syncwarp();
+      if (!mbar_wait(&v_empty[st], ph ^ 1, wc, DEV_TIMEOUT_ATTN_KV)) break;
+      if (lane == 0) {
+        mbar_expect_tx(&v_full[st], AT_TILE_BYTES);
+        tma_load_3d(v_smem + st * AT_TILE_BYTES, &tmQKV, &v_full[st], 2 * a.E + h * AT_D,
+                    j * AT_BN, b);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    constexpr uint32_t IDESC_S = make_idesc(1, 1, AT_BM, AT_BN, 0, 0);  // Q K^T, both K-major
+    constexpr uint32_t IDESC_O = make_idesc(1, 1, AT_BM, AT_D, 0, 1);   // P V, V is MN-major
+    const uint32_t s_tmem = tmem_base + AT_S_COL;
+    const uint32_t o_tmem = tmem_base + AT_O_COL;
+    const uint64_t q_desc = make_smem_desc_sw128(smem_u32(q_smem), 16, 1024);
+    bool ok = mbar_wait(q_full, 0, wc, DEV_TIMEOUT_ATTN_Q);
+    // S_0
+    if (ok) ok = mbar_wait(&k_full[0], 0, wc, DEV_TIMEOUT_ATTN_KV);
+    if (ok) {
+      tc_fence_after_sync();
+      if (lane == 0) {
+        const uint64_t k_desc = make_smem_desc_sw128(smem_u32(k_smem), 16, 1024);
+#pragma unroll
+        for (int k = 0; k < AT_D / 16; ++k)
+          mma_f16_ss(s_tmem, q_desc + 2 * k, k_desc + 2 * k, IDESC_S, k != 0);
+        mma_commit(&k_empty[0]);
+        mma_commit(s_full);
+      }
+      __syncwarp();
+    }
+    for (int j = 0; j < nkv && ok; ++j) {
+      const int st = j % AT_STAGES;
+      const uint32_t ph = (j / AT_STAGES) & 1;
+      // O += P_j V_j
+      if (!mbar_wait(p_ready, j & 1, wc, DEV_TIMEOUT_ATTN_P)) break;
+      if (!mbar_wait(&v_full[st], ph, wc, DEV_TIMEOUT_ATTN_KV)) break;
+      tc_fence_after_sync();
+      if (lane == 0) {
+        const uint64_t v_desc =
+            make_smem_desc_sw128(smem_u32(v_smem + st * AT_TILE_BYTES), 1024, 1024);
+#pragma unroll
+        for (int k = 0; k < AT_BN / 16; ++k) {
+          // 16 keys: 8 TMEM columns of packed bf16 pairs; 16 rows of V (128 B each)
+          mma_f16_ts(o_tmem, s_tmem + 8 * k, v_desc + static_cast<uint64_t>((k * 16 * 128) >> 4),
+                     IDESC_O, (j | k) != 0);
+        }
+        mma_commit(&v_empty[st]);
+        if (j == nkv - 1) mma_commit(o_full);
+      }
+      __syncwarp();
+      // S_{j+1}
+      if (j + 1 < nkv) {
+        const int st1 = (j + 1) % AT_STAGES;
+        const uint32_t ph1 = ((j + 1) / AT_STAGES) & 1;
+        if (!mbar_wait(&k_full[st1], ph1, wc, DEV_TIMEOUT_ATTN_KV)) break;
+        tc_fence_after_sync();
+        if (lane == 0) {
+          const uint64_t k_desc =
+              make_smem_desc_sw128(smem_u32(k_smem + st1 * AT_TILE_BYTES), 16, 1024);
+#pragma unroll
+          for (int k = 0; k < AT_D / 16; ++k)
+            mma_f16_ss(s_tmem, q_desc + 2 * k, k_desc + 2 * k, IDESC_S, k != 0);
+          mma_commit(&k_empty[st1]);
+          mma_commit(s_full);
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // ------------------------------ softmax + epilogue ------------------------
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+    const uint32_t s_tmem = lane_base + AT_S_COL;
+    const uint32_t o_tmem = lane_base + AT_O_COL;
+    const float c = a.scale_log2e;
+    float m_used = -INFINITY;  // running max (raw score units) the exponentials refer to
+    float l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nkv; ++j) {
+      if (!mbar_wait(s_full, j & 1, wc, DEV_TIMEOUT_ATTN_S)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int kv0 = j * AT_BN;
+      const bool tail = (kv0 + AT_BN > T);
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(s_tmem + ch * 32, r);
+        tmem_wait_ld();
+        if (tail) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (kv0 + ch * 32 + i < T) mx = fmaxf(mx, __uint_as_float(r[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
+      }
+      if (j == 0) {
+        m_used = mx;
+      } else {
+        // Rescale O only when the maximum moved by more than 2^8 in the exp2
+        // domain; otherwise keep exponentiating against the older maximum.
+        const bool need = (mx - m_used) * c > 8.0f;
+        if (__any_sync(0xffffffffu, need)) {
+          float alpha = 1.0f;
+          if (need) {
+            alpha = ex2_approx((m_used - mx) * c);
+            m_used = mx;
+            l *= alpha;
+          }
+          uint32_t o0[32], o1[32];
+          tmem_ld_32x32b_x32(o_tmem, o0);
+          tmem_ld_32x32b_x32(o_tmem + 32, o1);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            o0[i] = __float_as_uint(__uint_as_float(o0[i]) * alpha);
+            o1[i] = __float_as_uint(__uint_as_float(o1[i]) * alpha);
+          }
+          tmem_st_32x32b_x32(o_tmem, o0);
+          tmem_st_32x32b_x32(o_tmem + 32, o1);
+        }
+      }
+      const float mc = m_used * c;
+      // pass 2: P = exp2(S c - m c), packed to bf16 pairs over the S columns
+      float lsum = 0.f;
+#pragma unroll 1
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(s_tmem + ch * 32, r);
+        tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float p0 = ex2_approx(fmaf(__uint_as_float(r[2 * i]), c, -mc));
+          float p1 = ex2_approx(fmaf(__uint_as_float(r[2 * i + 1]), c, -mc));
+          if (tail) {
+            if (kv0 + ch * 32 + 2 * i >= T) p0 = 0.f;
+            if (kv0 + ch * 32 + 2 * i + 1 >= T) p1 = 0.f;
+          }
+          lsum += p0 + p1;
+          pk[i] = pack_bf16x2(p0, p1);
+        }
+        tmem_st_32x32b_x16(s_tmem + ch * 16, pk);
+      }
+      l += lsum;
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_ready);
+    }
+    if (ok && mbar_wait(o_full, 0, wc, DEV_TIMEOUT_ATTN_O)) {
+      tc_fence_after_sync();
+      uint32_t o0[32], o1[32];
+      tmem_ld_32x32b_x32(o_tmem, o0);
+      tmem_ld_32x32b_x32(o_tmem + 32, o1);
+      tmem_wait_ld();
+      const int t = q0 + row;
+      if (t < T) {
+        const float inv = 1.0f / l;
+        bf16* dst = nullptr;
+        if (t < a.Tc) {
+          if (a.out_c) dst = a.out_c + (static_cast<long>(b) * a.Tc + t) * a.E + h * AT_D;
+        } else {
+          dst = a.out_x + (static_cast<long>(b) * (T - a.Tc) + (t - a.Tc)) * a.E + h * AT_D;
+        }
+        if (dst) {
+          uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 u;
+            u.x = pack_bf16x2(__uint_as_float(o0[8 * i + 0]) * inv, __uint_as_float(o0[8 * i + 1]) * inv);
+            u.y = pack_bf16x2(__uint_as_float(o0[8 * i + 2]) * inv, __uint_as_float(o0[8 * i + 3]) * inv);
+            u.z = pack_bf16x2(__uint_as_float(o0[8 * i + 4]) * inv, __uint_as_float(o0[8 * i + 5]) * inv);
+            u.w = pack_bf16x2(__uint_as_float(o0[8 * i + 6]) * inv, __uint_as_float(o0[8 * i + 7]) * inv);
+            d4[i] = u;
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 u;
+            u.x = pack_bf16x2(__uint_as_float(o1[8 * i + 0]) * inv, __uint_as_float(o1[8 * i + 1]) * inv);
+            u.y = pack_bf16x2(__uint_as_float(o1[8 * i + 2]) * inv, __uint_as_float(o1[8 * i + 3]) * inv);
+            u.z = pack_bf16x2(__uint_as_float(o1[8 * i + 4]) * inv, __uint_as_float(o1[8 * i + 5]) * inv);
+            u.w = pack_bf16x2(__uint_as_float(o1[8 * i + 6]) * inv, __uint_as_float(o1[8 * i + 7]) * inv);
+            d4[4 + i] = u;
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*s_abort) drain_after_abort();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, AT_TMEM_COLS);
+  }
+}
+
+}  // namespace
+
+int launch_attention_bf16(const bf16* qkv, int B, int T, int NH, int Tc, bf16* out_c, bf16* out_x,
+                          float scale, int* dev_status, cudaStream_t stream) {
+  if (!qkv || !out_x || B <= 0 || T <= 0 || NH <= 0 || Tc < 0 || Tc > T ||
+      (reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(out_x) & 15) ||
+      (reinterpret_cast<uintptr_t>(out_c) & 15)) {
+    set_last_error("attention: invalid argument (B %d T %d NH %d Tc %d)", B, T, NH, Tc);
+    return ST_INVALID_ARG;
+  }
+  if (B > 65535 || NH > 65535) {
+    set_last_error("attention: B and NH must each be <= 65535");
+    return ST_UNSUPPORTED;
+  }
+  const int E = NH * AT_D;
+  CUtensorMap tm;
+  int rc = encode_tmap_3d(&tm, qkv, 2, 3ull * E, (uint64_t)T, (uint64_t)B, 3ull * E * 2,
+                          (uint64_t)T * 3ull * E * 2, AT_D, AT_BN, 1);
+  if (rc) return rc;
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES);
+    if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(attention)");
+    attr_done[dev] = true;
+  }
+  AttnArgs a;
+  a.B = B; a.T = T; a.NH = NH; a.Tc = Tc; a.E = E;
+  a.out_c = out_c; a.out_x = out_x;
+  a.scale_log2e = scale * 1.4426950408889634f;
+  a.status = dev_status;
+  const dim3 grid((T + AT_BM - 1) / AT_BM, NH, B);
+  attention_tcgen05_kernel<<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(tm, a);
+  return after_launch("attention_tcgen05_kernel");
+}
+
+}  // namespace sd3

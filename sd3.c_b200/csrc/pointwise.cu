@@ -1,0 +1,443 @@
+// HBM-bound kernels of the denoiser forward: LayerNorm + AdaLN modulation,
+// the skinny (M = batch) linears that produce the conditioning vector and all
+// AdaLN modulation vectors, timestep / position embeddings, patch gathering,
+// casts and transposes for weight packing, and a stand-alone per-head RMSNorm.
+// All of them are coalesced, 128-bit vectorised and warp-shuffle reduced.
+//
+// Reference counterparts: layernorm_forward_kernel6 (cuda/dit.cu:17-75) and
+// scale_and_shift3 (cuda/dit.cu:357-374) -> ln_modulate_kernel (one pass, both
+// modulations of a dual block at once); partial_linear_cuda launched 15x per
+// block with M = batch (cuda/dit.cu:102-354) -> skinny_linear_kernel, one
+// launch for every block's AdaLN vectors; sinusoidal_embedding
+// (modules.cpp:920-944); positional_embedding2D + crop
+// (modules.cpp:946-995); conv2d im2col side of PatchEmbedding
+// (modules.cpp:1037-1117); rmsnorm_key_query_kernel2 (cuda/dit.cu:384-447).
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace sd3 {
+
+namespace {
+
+// ----------------------------------------------------------------------------
+// LayerNorm + modulate.  One warp per row, the row lives in registers.
+// ----------------------------------------------------------------------------
+template <int MAXV, bool OUT_F32, bool DUAL>
+__global__ void __launch_bounds__(256)
+ln_modulate_kernel(const float* __restrict__ x, long rows, int T, int E, float eps,
+                   const float* __restrict__ shift1, const float* __restrict__ scale1,
+                   void* __restrict__ out1, const float* __restrict__ shift2,
+                   const float* __restrict__ scale2, void* __restrict__ out2, long mod_stride) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long row = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + warp;
+  if (row >= rows) return;
+  const int b = static_cast<int>(row / T);
+  const int nvec = E >> 2;
+  const float4* xr = reinterpret_cast<const float4*>(x + row * E);
+  float4 v[MAXV];
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j) {
+    const int i = lane + 32 * j;
+    if (i < nvec) {
+      v[j] = xr[i];
+      sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+    } else {
+      v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+  const float mean = warp_sum(sum) / static_cast<float>(E);
+  float sq = 0.f;
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j) {
+    const int i = lane + 32 * j;
+    if (i < nvec) {
+      const float a = v[j].x - mean, bq = v[j].y - mean, c = v[j].z - mean, d = v[j].w - mean;
+      sq += (a * a + bq * bq) + (c * c + d * d);
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(sq) / static_cast<float>(E) + eps);
+  const float4* sh1 = reinterpret_cast<const float4*>(shift1 + b * mod_stride);
+  const float4* sc1 = reinterpret_cast<const float4*>(scale1 + b * mod_stride);
+  const float4* sh2 = DUAL ? reinterpret_cast<const float4*>(shift2 + b * mod_stride) : nullptr;
+  const float4* sc2 = DUAL ? reinterpret_cast<const float4*>(scale2 + b * mod_stride) : nullptr;
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j) {
+    const int i = lane + 32 * j;
+    if (i < nvec) {
+      float4 n;
+      n.x = (v[j].x - mean) * rstd;
+      n.y = (v[j].y - mean) * rstd;
+      n.z = (v[j].z - mean) * rstd;
+      n.w = (v[j].w - mean) * rstd;
+      {
+        const float4 s = __ldg(sc1 + i), h = __ldg(sh1 + i);
+        float4 o;
+        o.x = fmaf(n.x, 1.f + s.x, h.x);
+        o.y = fmaf(n.y, 1.f + s.y, h.y);
+        o.z = fmaf(n.z, 1.f + s.z, h.z);
+        o.w = fmaf(n.w, 1.f + s.w, h.w);
+        if constexpr (OUT_F32) {
+          reinterpret_cast<float4*>(static_cast<float*>(out1) + row * E)[i] = o;
+        } else {
+          uint2 u;
+          u.x = pack_bf16x2(o.x, o.y);
+          u.y = pack_bf16x2(o.z, o.w);
+          reinterpret_cast<uint2*>(static_cast<bf16*>(out1) + row * E)[i] = u;
+        }
+      }
+      if constexpr (DUAL) {
+        const float4 s = __ldg(sc2 + i), h = __ldg(sh2 + i);
+        float4 o;
+        o.x = fmaf(n.x, 1.f + s.x, h.x);
+        o.y = fmaf(n.y, 1.f + s.y, h.y);
+        o.z = fmaf(n.z, 1.f + s.z, h.z);
+        o.w = fmaf(n.w, 1.f + s.w, h.w);
+        if constexpr (OUT_F32) {
+          reinterpret_cast<float4*>(static_cast<float*>(out2) + row * E)[i] = o;
+        } else {
+          uint2 u;
+          u.x = pack_bf16x2(o.x, o.y);
+          u.y = pack_bf16x2(o.z, o.w);
+          reinterpret_cast<uint2*>(static_cast<bf16*>(out2) + row * E)[i] = u;
+        }
+      }
+    }
+  }
+}
+
+template <int MAXV>
+int launch_ln_inst(const float* x, long rows, int T, int E, float eps, const float* shift1,
+                   const float* scale1, void* out1, const float* shift2, const float* scale2,
+                   void* out2, long mod_stride, int out_f32, cudaStream_t stream) {
+  const int wpb = 8;
+  const unsigned grid = static_cast<unsigned>((rows + wpb - 1) / wpb);
+  const bool dual = out2 != nullptr;
+#define SD3_LN_LAUNCH(F32, DUALV)                                                              \
+  ln_modulate_kernel<MAXV, F32, DUALV><<<grid, wpb * 32, 0, stream>>>(                         \
+      x, rows, T, E, eps, shift1, scale1, out1, shift2, scale2, out2, mod_stride)
+  if (out_f32) {
+    if (dual) SD3_LN_LAUNCH(true, true); else SD3_LN_LAUNCH(true, false);
+  } else {
+    if (dual) SD3_LN_LAUNCH(false, true); else SD3_LN_LAUNCH(false, false);
+  }
+#undef SD3_LN_LAUNCH
+  return after_launch("ln_modulate_kernel");
+}
+
+// ----------------------------------------------------------------------------
+// Skinny linear: each warp owns R output columns and a chunk of BC samples.
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ void load_w8(const bf16* p, float (&w)[8]) {
+  const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __bfloat1622float2(h[j]);
+    w[2 * j] = f.x;
+    w[2 * j + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void load_w8(const float* p, float (&w)[8]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p));
+  const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+  w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+}
+
+template <typename WT, int R, int BC>
+__global__ void __launch_bounds__(256)
+skinny_linear_kernel(const float* __restrict__ in, long ld_in, const WT* __restrict__ W,
+                     const float* __restrict__ bias, const float* __restrict__ add, long ld_add,
+                     float* __restrict__ out, long ld_out, int B, int N, int K, int act_out) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long n0 = (static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + warp) * R;
+  if (n0 >= N) return;
+  for (int b0 = 0; b0 < B; b0 += BC) {
+    float acc[R][BC];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int b = 0; b < BC; ++b) acc[r][b] = 0.f;
+    for (int k = lane * 8; k < K; k += 256) {
+      float w[R][8];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        if (n0 + r < N) {
+          load_w8(W + (n0 + r) * static_cast<long>(K) + k, w[r]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) w[r][j] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < BC; ++b) {
+        if (b0 + b < B) {
+          float xv[8];
+          load_w8(in + (b0 + b) * ld_in + k, xv);
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[r][b] = fmaf(xv[j], w[r][j], acc[r][b]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+#pragma unroll
+      for (int b = 0; b < BC; ++b) {
+        const float s = warp_sum(acc[r][b]);
+        if (lane == 0 && n0 + r < N && b0 + b < B) {
+          float o = s + (bias ? bias[n0 + r] : 0.f);
+          if (add) o += add[(b0 + b) * ld_add + n0 + r];
+          if (act_out == 1) o = o / (1.f + expf(-o));
+          out[(b0 + b) * ld_out + n0 + r] = o;
+        }
+      }
+    }
+  }
+}
+
+__global__ void sinusoidal_kernel(const float* __restrict__ t, float* __restrict__ out, int B,
+                                  int dim) {
+  const int half = dim / 2;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= B * half) return;
+  const int b = idx / half, i = idx % half;
+  // same fp32 operation order as the reference: exp(-ln(1e4) * i / half), then t * f
+  const float f = expf(-9.2103403719761836f * static_cast<float>(i) / static_cast<float>(half));
+  const float a = t[b] * f;
+  out[static_cast<long>(b) * dim + i] = cosf(a);
+  out[static_cast<long>(b) * dim + half + i] = sinf(a);
+}
+
+__global__ void pos_table_kernel(float* __restrict__ table, int h, int w, int E, int pmax,
+                                 int base_size) {
+  const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int q = E / 4;
+  const long total = static_cast<long>(h) * w * q;
+  if (idx >= total) return;
+  const int i = static_cast<int>(idx % q);
+  const long tok = idx / q;
+  const int s = static_cast<int>(tok % w), r = static_cast<int>(tok / w);
+  const int R = r + (pmax - h) / 2, S = s + (pmax - w) / 2;
+  const double denom = static_cast<double>(pmax) / static_cast<double>(base_size);
+  const double div = 1.0 / pow(10000.0, static_cast<double>(i) / (static_cast<double>(E) / 4.0));
+  const double ps = (static_cast<double>(S) / denom) * div;
+  const double pr = (static_cast<double>(R) / denom) * div;
+  float* o = table + tok * E;
+  o[i] = static_cast<float>(sin(ps));
+  o[q + i] = static_cast<float>(cos(ps));
+  o[2 * q + i] = static_cast<float>(sin(pr));
+  o[3 * q + i] = static_cast<float>(cos(pr));
+}
+
+template <typename IT, typename OT>
+__device__ __forceinline__ OT convert_elem(IT v);
+template <> __device__ __forceinline__ float convert_elem<float, float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 convert_elem<float, bf16>(float v) { return __float2bfloat16(v); }
+template <> __device__ __forceinline__ float convert_elem<bf16, float>(bf16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ bf16 convert_elem<bf16, bf16>(bf16 v) { return v; }
+
+template <typename IT, typename OT>
+__global__ void patchify_kernel(const IT* __restrict__ latent, OT* __restrict__ out, int B, int C,
+                                int H, int W, int p) {
+  const int hp = H / p, wp = W / p;
+  const int Kp = C * p * p;
+  const long total = static_cast<long>(B) * hp * wp * Kp;
+  const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int k = static_cast<int>(idx % Kp);
+  const long tok = idx / Kp;
+  const int s = static_cast<int>(tok % wp);
+  const int r = static_cast<int>((tok / wp) % hp);
+  const int b = static_cast<int>(tok / (static_cast<long>(wp) * hp));
+  const int pw = k % p, ph = (k / p) % p, c = k / (p * p);
+  const long src = ((static_cast<long>(b) * C + c) * H + (r * p + ph)) * W + (s * p + pw);
+  out[idx] = convert_elem<IT, OT>(latent[src]);
+}
+
+template <typename IT, typename OT>
+__global__ void cast_kernel(const IT* __restrict__ in, OT* __restrict__ out, long n) {
+  long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  for (; i < n; i += stride) out[i] = convert_elem<IT, OT>(in[i]);
+}
+
+template <typename IT, typename OT>
+__global__ void transpose_kernel(const IT* __restrict__ in, OT* __restrict__ out, int R, int C) {
+  __shared__ float tile[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    const int r = r0 + j, c = c0 + threadIdx.x;
+    tile[j][threadIdx.x] =
+        (r < R && c < C) ? convert_elem<IT, float>(in[static_cast<long>(r) * C + c]) : 0.f;
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    const int c = c0 + j, r = r0 + threadIdx.x;
+    if (r < R && c < C)
+      out[static_cast<long>(c) * R + r] = convert_elem<float, OT>(tile[threadIdx.x][j]);
+  }
+}
+
+template <typename XT>
+__global__ void rmsnorm_heads_kernel(XT* __restrict__ x, long ld, long rows, int col0, int nheads,
+                                     int D, const float* __restrict__ w, float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long unit = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + warp;
+  if (unit >= rows * nheads) return;
+  const long row = unit / nheads;
+  const int h = static_cast<int>(unit % nheads);
+  XT* p = x + row * ld + col0 + h * D;
+  float ss = 0.f;
+  for (int i = lane; i < D; i += 32) {
+    const float v = convert_elem<XT, float>(p[i]);
+    ss += v * v;
+  }
+  const float r = rsqrtf(warp_sum(ss) / static_cast<float>(D) + eps);
+  for (int i = lane; i < D; i += 32) {
+    const float v = convert_elem<XT, float>(p[i]) * r * (w ? w[i] : 1.f);
+    p[i] = convert_elem<float, XT>(v);
+  }
+}
+
+}  // namespace
+
+int launch_ln_modulate(const float* x, int B, int T, int E, float eps, const float* shift1,
+                       const float* scale1, void* out1, const float* shift2, const float* scale2,
+                       void* out2, long mod_stride, int out_f32, cudaStream_t stream) {
+  if (!x || !out1 || !shift1 || !scale1 || B <= 0 || T <= 0 || E <= 0 || (E & 3) ||
+      (mod_stride & 3)) {
+    set_last_error("ln_modulate: invalid argument (E %d must be a multiple of 4)", E);
+    return ST_INVALID_ARG;
+  }
+  if (out2 && (!shift2 || !scale2)) {
+    set_last_error("ln_modulate: second output needs its own shift/scale");
+    return ST_INVALID_ARG;
+  }
+  const long rows = static_cast<long>(B) * T;
+  const int nvec = E / 4;
+#define SD3_LN_CASE(MV)                                                                         \
+  if (nvec <= 32 * MV)                                                                          \
+    return launch_ln_inst<MV>(x, rows, T, E, eps, shift1, scale1, out1, shift2, scale2, out2,    \
+                              mod_stride, out_f32, stream)
+  SD3_LN_CASE(2);
+  SD3_LN_CASE(6);
+  SD3_LN_CASE(12);
+  SD3_LN_CASE(16);
+  SD3_LN_CASE(32);
+#undef SD3_LN_CASE
+  set_last_error("ln_modulate: E %d too large (max 4096)", E);
+  return ST_UNSUPPORTED;
+}
+
+int launch_skinny_linear(const float* in, long ld_in, const void* W, int w_f32, const float* bias,
+                         const float* add, long ld_add, float* out, long ld_out, int B, int N,
+                         int K, int act_out, cudaStream_t stream) {
+  if (!in || !W || !out || B <= 0 || N <= 0 || K <= 0 || (K & 7) || (ld_in & 3)) {
+    set_last_error("skinny_linear: invalid argument (K %d must be a multiple of 8)", K);
+    return ST_INVALID_ARG;
+  }
+  constexpr int R = 4, BC = 8, WPB = 8;
+  const long warps = (static_cast<long>(N) + R - 1) / R;
+  const unsigned grid = static_cast<unsigned>((warps + WPB - 1) / WPB);
+  if (w_f32)
+    skinny_linear_kernel<float, R, BC><<<grid, WPB * 32, 0, stream>>>(
+        in, ld_in, static_cast<const float*>(W), bias, add, ld_add, out, ld_out, B, N, K, act_out);
+  else
+    skinny_linear_kernel<bf16, R, BC><<<grid, WPB * 32, 0, stream>>>(
+        in, ld_in, static_cast<const bf16*>(W), bias, add, ld_add, out, ld_out, B, N, K, act_out);
+  return after_launch("skinny_linear_kernel");
+}
+
+int launch_sinusoidal(const float* t, float* out, int B, int dim, cudaStream_t stream) {
+  if (!t || !out || B <= 0 || dim <= 0 || (dim & 1)) {
+    set_last_error("sinusoidal: invalid argument");
+    return ST_INVALID_ARG;
+  }
+  const int n = B * (dim / 2);
+  sinusoidal_kernel<<<(n + 127) / 128, 128, 0, stream>>>(t, out, B, dim);
+  return after_launch("sinusoidal_kernel");
+}
+
+int launch_pos_table(float* table, int h, int w, int E, int pmax, int base_size,
+                     cudaStream_t stream) {
+  if (!table || h <= 0 || w <= 0 || E <= 0 || (E & 3) || h > pmax || w > pmax || base_size <= 0) {
+    set_last_error("pos_table: invalid argument (grid %dx%d, max %d, E %d)", h, w, pmax, E);
+    return ST_INVALID_ARG;
+  }
+  const long total = static_cast<long>(h) * w * (E / 4);
+  pos_table_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(table, h, w, E,
+                                                                                  pmax, base_size);
+  return after_launch("pos_table_kernel");
+}
+
+int launch_patchify(const void* latent, int in_f32, void* out, int out_f32, int B, int C, int H,
+                    int W, int p, cudaStream_t stream) {
+  if (!latent || !out || B <= 0 || C <= 0 || p <= 0 || H % p || W % p) {
+    set_last_error("patchify: invalid argument");
+    return ST_INVALID_ARG;
+  }
+  const long total = static_cast<long>(B) * C * H * W;
+  const unsigned grid = static_cast<unsigned>((total + 255) / 256);
+  if (in_f32 && out_f32)
+    patchify_kernel<float, float><<<grid, 256, 0, stream>>>((const float*)latent, (float*)out, B, C, H, W, p);
+  else if (in_f32)
+    patchify_kernel<float, bf16><<<grid, 256, 0, stream>>>((const float*)latent, (bf16*)out, B, C, H, W, p);
+  else if (out_f32)
+    patchify_kernel<bf16, float><<<grid, 256, 0, stream>>>((const bf16*)latent, (float*)out, B, C, H, W, p);
+  else
+    patchify_kernel<bf16, bf16><<<grid, 256, 0, stream>>>((const bf16*)latent, (bf16*)out, B, C, H, W, p);
+  return after_launch("patchify_kernel");
+}
+
+int launch_cast_f32_to_bf16(const float* in, bf16* out, long n, cudaStream_t stream) {
+  if (n <= 0) return ST_OK;
+  const unsigned grid = static_cast<unsigned>(n / 256 + 1 < 148 * 16 ? n / 256 + 1 : 148 * 16);
+  cast_kernel<float, bf16><<<grid, 256, 0, stream>>>(in, out, n);
+  return after_launch("cast_kernel");
+}
+
+int launch_cast_bf16_to_f32(const bf16* in, float* out, long n, cudaStream_t stream) {
+  if (n <= 0) return ST_OK;
+  const unsigned grid = static_cast<unsigned>(n / 256 + 1 < 148 * 16 ? n / 256 + 1 : 148 * 16);
+  cast_kernel<bf16, float><<<grid, 256, 0, stream>>>(in, out, n);
+  return after_launch("cast_kernel");
+}
+
+int launch_transpose(const void* in, int in_f32, void* out, int out_f32, int R, int C,
+                     cudaStream_t stream) {
+  if (!in || !out || R <= 0 || C <= 0) {
+    set_last_error("transpose: invalid argument");
+    return ST_INVALID_ARG;
+  }
+  const dim3 grid((C + 31) / 32, (R + 31) / 32), block(32, 8);
+  if (in_f32 && out_f32)
+    transpose_kernel<float, float><<<grid, block, 0, stream>>>((const float*)in, (float*)out, R, C);
+  else if (in_f32)
+    transpose_kernel<float, bf16><<<grid, block, 0, stream>>>((const float*)in, (bf16*)out, R, C);
+  else if (out_f32)
+    transpose_kernel<bf16, float><<<grid, block, 0, stream>>>((const bf16*)in, (float*)out, R, C);
+  else
+    transpose_kernel<bf16, bf16><<<grid, block, 0, stream>>>((const bf16*)in, (bf16*)out, R, C);
+  return after_launch("transpose_kernel");
+}
+
+int launch_rmsnorm_heads(void* x, int x_f32, long ld, long rows, int col0, int nheads, int D,
+                         const float* w, float eps, cudaStream_t stream) {
+  if (!x || rows <= 0 || nheads <= 0 || D <= 0) {
+    set_last_error("rmsnorm_heads: invalid argument");
+    return ST_INVALID_ARG;
+  }
+  const long units = rows * nheads;
+  const unsigned grid = static_cast<unsigned>((units + 7) / 8);
+  if (x_f32)
+    rmsnorm_heads_kernel<float><<<grid, 256, 0, stream>>>((float*)x, ld, rows, col0, nheads, D, w, eps);
+  else
+    rmsnorm_heads_kernel<bf16><<<grid, 256, 0, stream>>>((bf16*)x, ld, rows, col0, nheads, D, w, eps);
+  return after_launch("rmsnorm_heads_kernel");
+}
+
+}  // namespace sd3

@@ -1,0 +1,358 @@
+"""ctypes binding of libsd3_b200.so plus torch-tensor conveniences.
+
+PyTorch is used here for device memory and streams only; every computation
+goes through the C ABI declared in include/sd3_b200.h.  There is no CPU or
+PyTorch fallback: if the library is missing or a call fails, an exception is
+raised.
+
+The directory name of this package contains a dot, so it is loaded by path:
+
+    import importlib.util, os
+    spec = importlib.util.spec_from_file_location(
+        "sd3_b200", os.path.join(repo, "sd3.c_b200", "sd3_b200.py"))
+"""
+import ctypes
+import os
+from ctypes import c_char_p, c_float, c_int, c_int64, c_long, c_uint64, c_void_p, POINTER
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libsd3_b200.so")
+
+DTYPE_F32 = 0
+DTYPE_BF16 = 1
+PRECISION_BF16 = 0
+PRECISION_F32 = 1
+PRECISION_FP8 = 2
+ACT_NONE = 0
+ACT_GELU_TANH = 1
+
+
+class Sd3Error(RuntimeError):
+    pass
+
+
+class Config(ctypes.Structure):
+    _fields_ = [
+        ("num_layers", c_int),
+        ("dual_attention_mask", c_uint64),
+        ("pooled_dim", c_int),
+        ("captions_dim", c_int),
+        ("in_channels", c_int),
+        ("emb_dim", c_int),
+        ("attn_heads", c_int),
+        ("mlp_expand", c_int),
+        ("patch_size", c_int),
+        ("pos_embed_max_size", c_int),
+        ("base_height", c_int),
+        ("use_qk_norm", c_int),
+        ("last_discards_context", c_int),
+        ("precision", c_int),
+        ("block_only", c_int),
+    ]
+
+
+# name -> (restype, argtypes); must list every function include/sd3_b200.h declares
+PROTOTYPES = {
+    "sd3_abi_version": (c_int, []),
+    "sd3_last_error": (c_char_p, []),
+    "sd3_device_status": (c_int, [POINTER(c_int)]),
+    "sd3_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "sd3_linear_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "sd3_linear_gate_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "sd3_qkv_project": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "sd3_attention": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p]),
+    "sd3_attention_generic": (c_int, [c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_long, c_int, c_float, c_void_p]),
+    "sd3_layernorm_modulate": (c_int, [c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p]),
+    "sd3_skinny_linear": (c_int, [c_void_p, c_long, c_void_p, c_int, c_void_p, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int, c_void_p]),
+    "sd3_sinusoidal_embedding": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "sd3_pos_embed_table": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "sd3_patch_embed": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "sd3_pack_weight": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "sd3_cast": (c_int, [c_void_p, c_int, c_void_p, c_int, c_long, c_void_p]),
+    "sd3_rmsnorm_heads": (c_int, [c_void_p, c_int, c_long, c_long, c_int, c_int, c_int, c_void_p, c_float, c_void_p]),
+    "sd3_model_create": (c_int, [POINTER(Config), POINTER(c_void_p)]),
+    "sd3_model_destroy": (None, [c_void_p]),
+    "sd3_model_set_param": (c_int, [c_void_p, c_char_p, c_void_p, c_int, c_int, POINTER(c_int64), c_void_p]),
+    "sd3_model_finalize": (c_int, [c_void_p, POINTER(c_int)]),
+    "sd3_model_reserve": (c_int, [c_void_p, c_int, c_int, c_int, c_int]),
+    "sd3_dit_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "sd3_block_forward": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "sd3_launch_count": (c_long, [c_int]),
+}
+
+_lib = None
+
+
+def lib():
+    """Loads the shared library (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise Sd3Error(
+                "libsd3_b200.so not found at %s: run `python sd3.c_b200/build.py` "
+                "(there is no fallback path)" % LIB_PATH)
+        l = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(l, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = l
+    return _lib
+
+
+def check(rc, what=""):
+    if rc != 0:
+        msg = lib().sd3_last_error()
+        raise Sd3Error("%s failed (%d): %s" % (what or "sd3 call", rc, (msg or b"").decode()))
+
+
+def device_status():
+    st = c_int(0)
+    check(lib().sd3_device_status(ctypes.byref(st)), "sd3_device_status")
+    return st.value
+
+
+def assert_healthy():
+    st = device_status()
+    if st != 0:
+        raise Sd3Error("device status %d: a kernel gave up a bounded wait" % st)
+
+
+# ---------------------------------------------------------------------------
+# torch helpers
+# ---------------------------------------------------------------------------
+def _torch():
+    import torch
+    return torch
+
+
+def dtype_tag(t):
+    torch = _torch()
+    if t.dtype == torch.float32:
+        return DTYPE_F32
+    if t.dtype == torch.bfloat16:
+        return DTYPE_BF16
+    raise Sd3Error("unsupported dtype %s (float32 or bfloat16 expected)" % t.dtype)
+
+
+def ptr(t):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise Sd3Error("CUDA tensor expected")
+    if not t.is_contiguous():
+        raise Sd3Error("contiguous tensor expected")
+    return c_void_p(t.data_ptr())
+
+
+def stream_ptr():
+    return c_void_p(_torch().cuda.current_stream().cuda_stream)
+
+
+def pack_weight(w_in_out, out_dtype=None):
+    """(in, out) boundary weight -> packed (out, in) tensor of out_dtype (default bf16)."""
+    torch = _torch()
+    out_dtype = out_dtype or torch.bfloat16
+    K, N = w_in_out.shape
+    out = torch.empty((N, K), device=w_in_out.device, dtype=out_dtype)
+    check(lib().sd3_pack_weight(ptr(w_in_out), dtype_tag(w_in_out), ptr(out), dtype_tag(out), K, N,
+                                stream_ptr()), "sd3_pack_weight")
+    return out
+
+
+def cast(t, dtype):
+    torch = _torch()
+    out = torch.empty(t.shape, device=t.device, dtype=dtype)
+    check(lib().sd3_cast(ptr(t), dtype_tag(t), ptr(out), dtype_tag(out), t.numel(), stream_ptr()),
+          "sd3_cast")
+    return out
+
+
+def linear(x_bf16, w_nk_bf16, bias=None, act=ACT_NONE, out_dtype=None):
+    torch = _torch()
+    M, K = x_bf16.shape
+    N = w_nk_bf16.shape[0]
+    out = torch.empty((M, N), device=x_bf16.device, dtype=out_dtype or torch.bfloat16)
+    check(lib().sd3_linear(ptr(x_bf16), ptr(w_nk_bf16), ptr(bias), ptr(out), dtype_tag(out), M, N, K,
+                           act, stream_ptr()), "sd3_linear")
+    return out
+
+
+def linear_f32(x, w_nk, bias=None, act=ACT_NONE):
+    torch = _torch()
+    M, K = x.shape
+    N = w_nk.shape[0]
+    out = torch.empty((M, N), device=x.device, dtype=torch.float32)
+    check(lib().sd3_linear_f32(ptr(x), ptr(w_nk), ptr(bias), ptr(out), M, N, K, act, stream_ptr()),
+          "sd3_linear_f32")
+    return out
+
+
+def linear_gate_residual(x_bf16, w_nk_bf16, bias, gate, rows_per_sample, resid):
+    M, K = x_bf16.shape
+    N = w_nk_bf16.shape[0]
+    check(lib().sd3_linear_gate_residual(ptr(x_bf16), ptr(w_nk_bf16), ptr(bias), ptr(gate),
+                                         gate.stride(0), rows_per_sample, ptr(resid), M, N, K,
+                                         stream_ptr()), "sd3_linear_gate_residual")
+    return resid
+
+
+def qkv_project(x_bf16, w_nk_bf16, bias, wq, wk, eps, qkv_out, B, T_in, T_total, row_offset, E):
+    check(lib().sd3_qkv_project(ptr(x_bf16), ptr(w_nk_bf16), ptr(bias), ptr(wq), ptr(wk), eps,
+                                ptr(qkv_out), B, T_in, T_total, row_offset, E, stream_ptr()),
+          "sd3_qkv_project")
+    return qkv_out
+
+
+def attention(qkv_bf16, B, T, num_heads, Tc, scale, want_context=True):
+    torch = _torch()
+    E = num_heads * 64
+    out_c = torch.empty((B, Tc, E), device=qkv_bf16.device, dtype=torch.bfloat16) if (want_context and Tc > 0) else None
+    out_x = torch.empty((B, T - Tc, E), device=qkv_bf16.device, dtype=torch.bfloat16)
+    check(lib().sd3_attention(ptr(qkv_bf16), B, T, num_heads, Tc, ptr(out_c), ptr(out_x), scale,
+                              stream_ptr()), "sd3_attention")
+    return out_c, out_x
+
+
+def attention_generic(q, k, v, num_heads, scale=None, out_dtype=None):
+    torch = _torch()
+    B, T, C = q.shape
+    D = C // num_heads
+    scale = scale if scale is not None else D ** -0.5
+    out = torch.empty((B, T, C), device=q.device, dtype=out_dtype or q.dtype)
+    check(lib().sd3_attention_generic(ptr(q), ptr(k), ptr(v), C, dtype_tag(q), B, T, num_heads, D,
+                                      ptr(out), C, dtype_tag(out), scale, stream_ptr()),
+          "sd3_attention_generic")
+    return out
+
+
+def layernorm_modulate(x, B, T, E, eps, shift1, scale1, shift2=None, scale2=None, mod_stride=None,
+                       out_dtype=None):
+    torch = _torch()
+    out_dtype = out_dtype or torch.bfloat16
+    out1 = torch.empty((B * T, E), device=x.device, dtype=out_dtype)
+    out2 = torch.empty((B * T, E), device=x.device, dtype=out_dtype) if shift2 is not None else None
+    ms = mod_stride if mod_stride is not None else shift1.stride(0)
+    check(lib().sd3_layernorm_modulate(ptr(x), B, T, E, eps, c_void_p(shift1.data_ptr()),
+                                       c_void_p(scale1.data_ptr()), ptr(out1),
+                                       c_void_p(shift2.data_ptr()) if shift2 is not None else None,
+                                       c_void_p(scale2.data_ptr()) if scale2 is not None else None,
+                                       ptr(out2), ms, dtype_tag(out1), stream_ptr()),
+          "sd3_layernorm_modulate")
+    return out1, out2
+
+
+def skinny_linear(inp, w_nk, bias=None, add=None, act=0):
+    torch = _torch()
+    B, K = inp.shape
+    N = w_nk.shape[0]
+    out = torch.empty((B, N), device=inp.device, dtype=torch.float32)
+    check(lib().sd3_skinny_linear(ptr(inp), K, ptr(w_nk), dtype_tag(w_nk), ptr(bias), ptr(add),
+                                  N if add is not None else 0, ptr(out), N, B, N, K, act,
+                                  stream_ptr()), "sd3_skinny_linear")
+    return out
+
+
+def sinusoidal_embedding(t, dim):
+    torch = _torch()
+    out = torch.empty((t.shape[0], dim), device=t.device, dtype=torch.float32)
+    check(lib().sd3_sinusoidal_embedding(ptr(t), ptr(out), t.shape[0], dim, stream_ptr()),
+          "sd3_sinusoidal_embedding")
+    return out
+
+
+def pos_embed_table(h, w, E, pos_max, base_size, device="cuda"):
+    torch = _torch()
+    out = torch.empty((h * w, E), device=device, dtype=torch.float32)
+    check(lib().sd3_pos_embed_table(ptr(out), h, w, E, pos_max, base_size, stream_ptr()),
+          "sd3_pos_embed_table")
+    return out
+
+
+def patch_embed(latent, w_nk_bf16, bias, pos_table, patch, E):
+    torch = _torch()
+    B, C, H, W = latent.shape
+    hp, wp = H // patch, W // patch
+    out = torch.empty((B * hp * wp, E), device=latent.device, dtype=torch.float32)
+    scratch = torch.empty((B * hp * wp, C * patch * patch), device=latent.device, dtype=torch.bfloat16)
+    check(lib().sd3_patch_embed(ptr(latent), dtype_tag(latent), ptr(w_nk_bf16), ptr(bias),
+                                ptr(pos_table), ptr(out), ptr(scratch), B, C, H, W, patch, E,
+                                stream_ptr()), "sd3_patch_embed")
+    return out
+
+
+def rmsnorm_heads(x, col0, nheads, head_dim, w, eps):
+    rows = x.numel() // x.shape[-1]
+    check(lib().sd3_rmsnorm_heads(ptr(x), dtype_tag(x), x.shape[-1], rows, col0, nheads, head_dim,
+                                  ptr(w), eps, stream_ptr()), "sd3_rmsnorm_heads")
+    return x
+
+
+# ---------------------------------------------------------------------------
+# model-level wrapper
+# ---------------------------------------------------------------------------
+class Model:
+    """Owns an sd3_model handle.  `params` follows the reference convention:
+    named_parameters() keys, 2-D weights transposed to (in, out)
+    (module_tests/DiT.py:25-31)."""
+
+    def __init__(self, num_layers, dual_attention_layers, pooled_dim, captions_dim, in_channels,
+                 emb_dim, attn_heads, mlp_expand, patch_size, pos_embed_max_size, base_height,
+                 use_qk_norm=True, precision=PRECISION_BF16, last_discards_context=True,
+                 block_only=False):
+        mask = 0
+        for l in dual_attention_layers:
+            mask |= 1 << int(l)
+        self.cfg = Config(num_layers, mask, pooled_dim, captions_dim, in_channels, emb_dim,
+                          attn_heads, mlp_expand, patch_size, pos_embed_max_size, base_height,
+                          int(bool(use_qk_norm)), int(bool(last_discards_context)), precision,
+                          int(bool(block_only)))
+        self.handle = c_void_p()
+        check(lib().sd3_model_create(ctypes.byref(self.cfg), ctypes.byref(self.handle)),
+              "sd3_model_create")
+
+    def close(self):
+        if self.handle:
+            lib().sd3_model_destroy(self.handle)
+            self.handle = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_param(self, name, tensor):
+        shape = (c_int64 * tensor.dim())(*tensor.shape)
+        check(lib().sd3_model_set_param(self.handle, name.encode(), ptr(tensor), dtype_tag(tensor),
+                                        tensor.dim(), shape, stream_ptr()),
+              "sd3_model_set_param(%s)" % name)
+
+    def load(self, params, prefix=""):
+        for name, t in params.items():
+            self.set_param(prefix + name, t.contiguous())
+        missing = c_int(0)
+        check(lib().sd3_model_finalize(self.handle, ctypes.byref(missing)), "sd3_model_finalize")
+        return self
+
+    def reserve(self, B, Tc, H, W):
+        check(lib().sd3_model_reserve(self.handle, B, Tc, H, W), "sd3_model_reserve")
+
+    def forward(self, pooled, captions, latent, timesteps, out=None):
+        torch = _torch()
+        B, C, H, W = latent.shape
+        Tc = captions.shape[1]
+        if out is None:
+            out = torch.empty_like(latent)
+        t32 = timesteps.to(torch.float32).contiguous()
+        check(lib().sd3_dit_forward(self.handle, ptr(pooled), ptr(captions), ptr(latent), ptr(t32),
+                                    ptr(out), dtype_tag(latent), B, Tc, H, W, stream_ptr()),
+              "sd3_dit_forward")
+        return out
+
+    def block_forward(self, layer, y, c, x):
+        B, Tc, E = c.shape
+        Tx = x.shape[1]
+        check(lib().sd3_block_forward(self.handle, layer, ptr(y), ptr(c), ptr(x), B, Tc, Tx,
+                                      stream_ptr()), "sd3_block_forward")
+        return c, x
