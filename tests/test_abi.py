@@ -1,0 +1,47 @@
+"""The C-ABI library: builds, loads, and exports every symbol the header
+declares.  No compute calls here (no GPU needed)."""
+import ctypes
+import os
+import re
+
+from conftest import REPO, load_binding
+
+
+def declared_functions():
+    text = open(os.path.join(REPO, "include", "sd3_b200.h")).read()
+    return sorted(set(re.findall(r"SD3_API\s+[A-Za-z_ \*]+?\b(sd3_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_functions():
+    names = declared_functions()
+    assert len(names) >= 20
+    for must in ("sd3_dit_forward", "sd3_block_forward", "sd3_linear", "sd3_attention",
+                 "sd3_layernorm_modulate", "sd3_last_error"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol():
+    s = load_binding()
+    assert os.path.exists(s.LIB_PATH), "run python sd3.c_b200/build.py"
+    lib = ctypes.CDLL(s.LIB_PATH)
+    for name in declared_functions():
+        assert hasattr(lib, name), name
+
+
+def test_binding_covers_header():
+    s = load_binding()
+    assert sorted(s.PROTOTYPES) == declared_functions()
+    assert s.lib().sd3_abi_version() == 1
+
+
+def test_host_side_argument_errors_need_no_gpu():
+    s = load_binding()
+    lib = s.lib()
+    # invalid arguments are rejected before any CUDA call
+    assert lib.sd3_linear(None, None, None, None, 7, 1, 1, 1, 0, None) == -1
+    assert b"sd3_linear" in lib.sd3_last_error()
+    assert lib.sd3_model_create(None, None) == -1
+    cfg = s.Config(0, 0, 8, 8, 16, 64, 1, 4, 2, 16, 16, 1, 1, 0, 0)
+    h = ctypes.c_void_p()
+    assert lib.sd3_model_create(ctypes.byref(cfg), ctypes.byref(h)) == -1  # num_layers 0
+    assert lib.sd3_cast(None, 0, None, 1, 4, None) == -1

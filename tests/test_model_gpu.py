@@ -1,0 +1,177 @@
+"""Block- and model-level parity on the GPU through the C ABI.
+
+Golden fixtures (tests/golden, produced by the reference's PyTorch modules)
+pin both precision modes; larger seeded cases are checked against the CPU
+oracle.  Tolerances are the north-star ones: fp32 mode max-abs <= 1e-4 per
+module; bf16 mode relative L2 <= 1e-2 against the fp32 result on the same
+(bf16-representable) weights and inputs."""
+import pytest
+import torch
+
+from conftest import golden
+from oracle import mmdit_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_l2(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return ((a - b).norm() / (b.norm() + 1e-30)).item()
+
+
+def to_dev(params, dtype):
+    return {k: v.to(dtype).cuda().contiguous() for k, v in params.items()}
+
+
+def run_block(sd3, g, precision):
+    cfg = g["config"]
+    dtype = torch.float32 if precision == sd3.PRECISION_F32 else torch.bfloat16
+    m = sd3.Model(1, [0] if cfg["use_dual_attention"] else [], 0, 0, 0, cfg["emb_dim"],
+                  cfg["attn_heads"], cfg["mlp_expand"], 0, 0, 0, cfg["use_qk_norm"], precision,
+                  last_discards_context=cfg["discard_context"], block_only=True)
+    m.load(to_dev(g["params"], dtype), prefix="transformer.0.")
+    y = g["y"].float().cuda().contiguous()
+    c = g["c"].float().cuda().contiguous()
+    x = g["x"].float().cuda().contiguous()
+    m.block_forward(0, y, c, x)
+    torch.cuda.synchronize()
+    assert sd3.device_status() == 0
+    m.close()
+    return c, x
+
+
+@pytest.mark.parametrize("name", ["block_dual.pt", "block_last.pt", "block_plain_hd32.pt"])
+def test_block_golden_fp32(sd3, name):
+    g = golden(name)
+    c, x = run_block(sd3, g, sd3.PRECISION_F32)
+    assert (x.cpu() - g["x_out"]).abs().max().item() < 1e-4
+    if not g["config"]["discard_context"]:
+        assert (c.cpu() - g["c_out"]).abs().max().item() < 1e-4
+
+
+@pytest.mark.parametrize("name", ["block_dual.pt", "block_last.pt", "block_plain_hd32.pt"])
+def test_block_golden_bf16(sd3, name):
+    g = golden(name)
+    c, x = run_block(sd3, g, sd3.PRECISION_BF16)
+    assert rel_l2(x, g["x_out"]) < 1e-2
+    if not g["config"]["discard_context"]:
+        assert rel_l2(c, g["c_out"]) < 1e-2
+
+
+def make_model(sd3, cfg, params, precision):
+    dtype = torch.float32 if precision == sd3.PRECISION_F32 else torch.bfloat16
+    m = sd3.Model(cfg["num_layers"], cfg["dual_attention_layers"], cfg["pooled_dim"],
+                  cfg["captions_dim"], cfg["in_channels"], cfg["emb_dim"], cfg["attn_heads"],
+                  cfg["mlp_expand"], cfg["patch_size"], cfg["pos_embed_max_size"],
+                  cfg["base_height"], True, precision)
+    m.load(to_dev(params, dtype))
+    return m
+
+
+@pytest.mark.parametrize("precision_name", ["f32", "bf16"])
+def test_model_golden(sd3, precision_name):
+    g = golden("model_toy.pt")
+    precision = sd3.PRECISION_F32 if precision_name == "f32" else sd3.PRECISION_BF16
+    dtype = torch.float32 if precision_name == "f32" else torch.bfloat16
+    m = make_model(sd3, g["config"], g["params"], precision)
+    out = m.forward(g["pooled"].to(dtype).cuda(), g["captions"].to(dtype).cuda(),
+                    g["latent"].to(dtype).cuda(), g["timesteps"].cuda())
+    torch.cuda.synchronize()
+    assert sd3.device_status() == 0
+    if precision_name == "f32":
+        assert (out.cpu() - g["out"]).abs().max().item() < 1e-4
+    else:
+        assert rel_l2(out, g["out"]) < 1e-2
+    # a second call on the same handle gives the same bits (no state carried over)
+    out2 = m.forward(g["pooled"].to(dtype).cuda(), g["captions"].to(dtype).cuda(),
+                     g["latent"].to(dtype).cuda(), g["timesteps"].cuda())
+    assert torch.equal(out, out2)
+    m.close()
+
+
+def test_missing_and_unknown_parameters(sd3):
+    g = golden("model_toy.pt")
+    cfg = g["config"]
+    m = sd3.Model(cfg["num_layers"], cfg["dual_attention_layers"], cfg["pooled_dim"],
+                  cfg["captions_dim"], cfg["in_channels"], cfg["emb_dim"], cfg["attn_heads"],
+                  cfg["mlp_expand"], cfg["patch_size"], cfg["pos_embed_max_size"],
+                  cfg["base_height"], True, sd3.PRECISION_BF16)
+    p = to_dev(g["params"], torch.bfloat16)
+    with pytest.raises(sd3.Sd3Error):
+        m.set_param("transformer.0.not_a_layer.weight", p["linear_out.weight"])
+    with pytest.raises(sd3.Sd3Error):  # wrong shape
+        m.set_param("linear_out.weight", p["captions_linear.weight"])
+    first = dict(list(p.items())[:5])
+    with pytest.raises(sd3.Sd3Error, match="missing"):
+        m.load(first)
+    m.close()
+
+
+def test_config1_single_dual_block_fp32(sd3):
+    """BASELINE config 1: one dual MMDiT-X block, fp32, batch 1, E 1536, 24 heads,
+    256 image + 77 context tokens, weights N(0, 0.02), biases 0, seed 0; the
+    conditioning vector comes from a timestep-500 sinusoidal embedding plus a
+    pooled N(0,1) vector through SiLU."""
+    torch.manual_seed(0)
+    E, NH = 1536, 24
+    shapes = O.block_param_shapes(E, 4, 64, True, False, True)
+    p = O.random_params(shapes, seed=0, std=0.02)
+    gen = torch.Generator().manual_seed(0)
+    x = torch.randn(1, 256, E, generator=gen)
+    c = torch.randn(1, 77, E, generator=gen)
+    # y = silu(Linear-SiLU-Linear(sinusoidal(500)) + pooled), cf. module_tests/modules.py:403-407
+    w1 = torch.randn(256, E, generator=gen) * 0.02
+    w2 = torch.randn(E, E, generator=gen) * 0.02
+    pooled = torch.randn(1, E, generator=gen)
+    emb = O.sinusoidal_embedding(torch.tensor([500.0]), 256)
+    y = torch.nn.functional.silu(torch.nn.functional.silu(emb @ w1) @ w2 + pooled)
+    c_ref, x_ref = O.dit_block(x, c, y, p, NH, True, True, False)
+    for precision, check in ((sd3.PRECISION_F32, "abs"), (sd3.PRECISION_BF16, "rel")):
+        dtype = torch.float32 if precision == sd3.PRECISION_F32 else torch.bfloat16
+        m = sd3.Model(1, [0], 0, 0, 0, E, NH, 4, 0, 0, 0, True, precision,
+                      last_discards_context=False, block_only=True)
+        m.load(to_dev(p, dtype), prefix="transformer.0.")
+        cc, xx = c.cuda().clone(), x.cuda().clone()
+        m.block_forward(0, y.cuda(), cc, xx)
+        torch.cuda.synchronize()
+        assert sd3.device_status() == 0
+        if check == "abs":
+            assert (xx.cpu() - x_ref).abs().max().item() < 1e-4
+            assert (cc.cpu() - c_ref).abs().max().item() < 1e-4
+        else:
+            # bf16 weights are rounded here, so compare against the oracle on rounded weights
+            pr = {k: v.bfloat16().float() for k, v in p.items()}
+            c_r, x_r = O.dit_block(x, c, y, pr, NH, True, True, False)
+            assert rel_l2(xx, x_r) < 1e-2
+            assert rel_l2(cc, c_r) < 1e-2
+        m.close()
+
+
+def test_config2_full_model_bf16(sd3):
+    """BASELINE config 2: full SD3.5-medium DiT forward, bf16, batch 1, 512x512
+    (latent 16x64x64 -> 1024 image tokens), 333 context tokens x 4096, pooled
+    2048, 24 blocks (first 13 dual), weights N(0, 0.02), seed 1.  Checked
+    against the fp32 CPU oracle on the same bf16-rounded weights and inputs."""
+    cfgm = O.SD35_MEDIUM
+    shapes = O.model_param_shapes(cfgm["num_layers"], cfgm["dual_layers"], cfgm["in_dim"], cfgm["E"],
+                                  cfgm["pooled_dim"], cfgm["captions_dim"], cfgm["patch"],
+                                  cfgm["attn_heads"], cfgm["mlp_expand"])
+    p = O.random_params(shapes, seed=1, std=0.02, dtype=torch.bfloat16)
+    gen = torch.Generator().manual_seed(1)
+    latent = torch.randn(1, 16, 64, 64, generator=gen).bfloat16()
+    captions = torch.randn(1, 333, 4096, generator=gen).bfloat16()
+    pooled = torch.randn(1, 2048, generator=gen).bfloat16()
+    t = (torch.rand(1, generator=gen) * 1000).bfloat16().float()
+    m = sd3.Model(24, range(13), 2048, 4096, 16, 1536, 24, 4, 2, 384, 128, True, sd3.PRECISION_BF16)
+    m.load({k: v.cuda() for k, v in p.items()})
+    out = m.forward(pooled.cuda(), captions.cuda(), latent.cuda(), t.cuda())
+    torch.cuda.synchronize()
+    assert sd3.device_status() == 0
+    m.close()
+    pf = {k: v.float() for k, v in p.items()}
+    with torch.no_grad():
+        ref = O.dit_forward(pooled.float(), captions.float(), latent.float(), t, pf, 24, range(13), 24,
+                            2, 384, 128, True)
+    r = rel_l2(out, ref)
+    print("config2 rel_l2", r)
+    assert r < 1e-2

@@ -1,0 +1,207 @@
+"""Per-operator parity on the GPU through the C ABI, each op against a plain
+PyTorch fp32 evaluation of the same formula on the same seeded inputs.
+Tolerances: fp32 kernels max-abs <= 1e-4 (north-star per-module bound);
+bf16-operand kernels rel-L2 <= 1e-2 (they are far tighter in practice because
+accumulation is fp32 and the inputs here are already bf16-representable)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_l2(a, b):
+    a, b = a.double(), b.double()
+    return ((a - b).norm() / (b.norm() + 1e-30)).item()
+
+
+@pytest.fixture(autouse=True)
+def _healthy(sd3):
+    yield
+    assert sd3.device_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (77, 1536, 1536), (333, 4608, 1536),
+                                   (4096, 1536, 1536), (1000, 6144, 1536), (1000, 1536, 6144),
+                                   (200, 384, 192), (500, 64, 1536), (130, 1000, 72), (1, 8, 8)])
+def test_linear_bf16(sd3, M, N, K):
+    torch.manual_seed(M + N + K)
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    b = torch.randn(N, device="cuda")
+    out = sd3.linear(x, w, b, out_dtype=torch.float32)
+    ref = x.float() @ w.float().t() + b
+    assert rel_l2(out, ref) < 1e-4
+    out16 = sd3.linear(x, w, b)
+    assert rel_l2(out16, ref) < 1e-2
+    g = sd3.linear(x, w, b, act=sd3.ACT_GELU_TANH, out_dtype=torch.float32)
+    assert rel_l2(g, torch.nn.functional.gelu(ref, approximate="tanh")) < 1e-4
+
+
+def test_linear_rejects_bad_shapes(sd3):
+    x = torch.zeros(16, 12, device="cuda", dtype=torch.bfloat16)  # K = 12: pitch not 16-byte multiple
+    w = torch.zeros(8, 12, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(sd3.Sd3Error):
+        sd3.linear(x, w)
+
+
+@pytest.mark.parametrize("M,N,K", [(77, 1536, 1536), (130, 100, 70), (5, 3, 2)])
+def test_linear_f32_exact(sd3, M, N, K):
+    torch.manual_seed(1)
+    x = torch.randn(M, K, device="cuda")
+    w = torch.randn(N, K, device="cuda") * 0.05
+    b = torch.randn(N, device="cuda")
+    ref = (x.double() @ w.double().t() + b.double()).float()
+    assert (sd3.linear_f32(x, w, b) - ref).abs().max().item() < 1e-4
+    g = sd3.linear_f32(x, w, b, act=sd3.ACT_GELU_TANH)
+    assert (g - torch.nn.functional.gelu(ref, approximate="tanh")).abs().max().item() < 1e-4
+
+
+def test_gate_residual(sd3):
+    torch.manual_seed(2)
+    B, T, N, K = 3, 200, 1536, 512
+    x = torch.randn(B * T, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    b = torch.randn(N, device="cuda")
+    mod = torch.randn(B, 5 * N, device="cuda")
+    gate = mod[:, N:2 * N]
+    resid = torch.randn(B * T, N, device="cuda")
+    r0 = resid.clone()
+    sd3.check(sd3.lib().sd3_linear_gate_residual(
+        sd3.ptr(x), sd3.ptr(w), sd3.ptr(b), gate.data_ptr(), mod.stride(0), T, sd3.ptr(resid),
+        B * T, N, K, sd3.stream_ptr()))
+    ref = r0 + ((x.float() @ w.float().t() + b).view(B, T, N) * gate[:, None, :]).view(B * T, N)
+    assert rel_l2(resid, ref) < 1e-4
+
+
+@pytest.mark.parametrize("E,B,Tin,Tt,off", [(192, 2, 100, 150, 50), (1536, 2, 77, 333, 0), (128, 1, 130, 130, 0)])
+def test_qkv_project_norm_and_concat(sd3, E, B, Tin, Tt, off):
+    torch.manual_seed(3)
+    x = torch.randn(B * Tin, E, device="cuda").bfloat16()
+    w = (torch.randn(3 * E, E, device="cuda") * 0.1).bfloat16()
+    b = torch.randn(3 * E, device="cuda")
+    wq = torch.randn(64, device="cuda")
+    wk = torch.randn(64, device="cuda")
+    qkv = torch.zeros(B, Tt, 3 * E, device="cuda", dtype=torch.bfloat16)
+    sd3.qkv_project(x, w, b, wq, wk, 1e-6, qkv, B, Tin, Tt, off, E)
+    y = (x.float() @ w.float().t() + b).view(B, Tin, 3, E // 64, 64)
+
+    def rms(v, wt):
+        return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-6) * wt
+
+    ref = torch.stack([rms(y[:, :, 0], wq), rms(y[:, :, 1], wk), y[:, :, 2]], 2).reshape(B, Tin, 3 * E)
+    assert rel_l2(qkv[:, off:off + Tin], ref) < 1e-2
+    # rows outside [off, off+Tin) are not touched
+    assert qkv[:, :off].abs().max().item() == 0 if off else True
+    assert qkv[:, off + Tin:].abs().max().item() == 0 if off + Tin < Tt else True
+
+
+@pytest.mark.parametrize("B,T,NH,Tc", [(1, 128, 1, 0), (1, 1, 1, 0), (1, 333, 2, 77), (2, 1357, 3, 333),
+                                       (1, 640, 24, 128), (1, 4429, 2, 333), (3, 129, 1, 129)])
+def test_attention_bf16(sd3, B, T, NH, Tc):
+    torch.manual_seed(T)
+    E = NH * 64
+    qkv = torch.randn(B, T, 3 * E, device="cuda").bfloat16()
+    if Tc == T:
+        pytest.skip("all-context split has no image rows")
+    oc, ox = sd3.attention(qkv, B, T, NH, Tc, 0.125)
+    q, k, v = [t.view(B, T, NH, 64).transpose(1, 2).float() for t in qkv.chunk(3, -1)]
+    ref = torch.nn.functional.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, T, E)
+    got = torch.cat([oc, ox], 1) if oc is not None else ox
+    assert rel_l2(got, ref) < 1e-2
+    # dropping the context rows must not change the image rows
+    _, ox2 = sd3.attention(qkv, B, T, NH, Tc, 0.125, want_context=False)
+    assert torch.equal(ox, ox2)
+
+
+def test_attention_large_scores_stay_finite(sd3):
+    # peaked softmax: exercises the running-max update / O rescale path
+    torch.manual_seed(5)
+    B, T, NH = 1, 700, 2
+    qkv = (torch.randn(B, T, 3 * NH * 64, device="cuda") * 6).bfloat16()
+    _, ox = sd3.attention(qkv, B, T, NH, 0, 0.125)
+    q, k, v = [t.view(B, T, NH, 64).transpose(1, 2).float() for t in qkv.chunk(3, -1)]
+    ref = torch.nn.functional.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, T, -1)
+    assert torch.isfinite(ox.float()).all()
+    assert rel_l2(ox, ref) < 2e-2
+
+
+@pytest.mark.parametrize("B,T,NH,D", [(2, 333, 24, 64), (1, 100, 2, 128), (2, 50, 3, 32), (1, 7, 1, 16)])
+def test_attention_generic_f32(sd3, B, T, NH, D):
+    torch.manual_seed(6)
+    q, k, v = [torch.randn(B, T, NH * D, device="cuda") for _ in range(3)]
+    o = sd3.attention_generic(q, k, v, NH)
+    qq, kk, vv = [t.view(B, T, NH, D).transpose(1, 2).double() for t in (q, k, v)]
+    ref = torch.nn.functional.scaled_dot_product_attention(qq, kk, vv).transpose(1, 2).reshape(B, T, NH * D)
+    assert (o - ref.float()).abs().max().item() < 1e-4
+
+
+@pytest.mark.parametrize("B,T,E", [(2, 77, 1536), (1, 5, 256), (3, 33, 768), (1, 2, 64), (1, 3, 2048)])
+def test_layernorm_modulate(sd3, B, T, E):
+    torch.manual_seed(7)
+    x = torch.randn(B * T, E, device="cuda") * 2 + 0.3
+    mod = torch.randn(B, 9 * E, device="cuda") * 0.3
+    o1, o2 = sd3.layernorm_modulate(x, B, T, E, 1e-6, mod[:, 0:E], mod[:, E:2 * E],
+                                    mod[:, 6 * E:7 * E], mod[:, 7 * E:8 * E], out_dtype=torch.float32)
+    ln = torch.nn.functional.layer_norm(x, (E,), eps=1e-6).view(B, T, E)
+    r1 = (ln * (1 + mod[:, None, E:2 * E]) + mod[:, None, 0:E]).view(B * T, E)
+    r2 = (ln * (1 + mod[:, None, 7 * E:8 * E]) + mod[:, None, 6 * E:7 * E]).view(B * T, E)
+    assert (o1 - r1).abs().max().item() < 1e-4
+    assert (o2 - r2).abs().max().item() < 1e-4
+    b1, _ = sd3.layernorm_modulate(x, B, T, E, 1e-6, mod[:, 0:E], mod[:, E:2 * E])
+    assert rel_l2(b1, r1) < 1e-2
+
+
+@pytest.mark.parametrize("B,N,K", [(2, 1536, 256), (8, 27652, 1536), (11, 1536, 2048), (1, 3, 8)])
+def test_skinny_linear(sd3, B, N, K):
+    torch.manual_seed(8)
+    inp = torch.randn(B, K, device="cuda")
+    w = torch.randn(N, K, device="cuda") * 0.05
+    b = torch.randn(N, device="cuda")
+    add = torch.randn(B, N, device="cuda")
+    o = sd3.skinny_linear(inp, w, b, add, act=1)
+    ref = torch.nn.functional.silu(inp.double() @ w.double().t() + b + add).float()
+    assert (o - ref).abs().max().item() < 1e-4
+    o = sd3.skinny_linear(inp, w.bfloat16(), b)
+    ref = (inp.double() @ w.bfloat16().double().t() + b).float()
+    assert (o - ref).abs().max().item() < 1e-4
+
+
+def test_sinusoidal_and_pos_table(sd3):
+    from oracle import mmdit_oracle as O
+    t = torch.tensor([0.0, 0.5, 500.0, 999.0, 37.25], device="cuda")
+    o = sd3.sinusoidal_embedding(t, 256)
+    assert (o.cpu() - O.sinusoidal_embedding(t.cpu(), 256)).abs().max().item() < 1e-4
+    for (h, w, E, pmax, base) in [(64, 64, 1536, 384, 64), (6, 10, 128, 24, 8), (1, 1, 64, 16, 8)]:
+        tab = sd3.pos_embed_table(h, w, E, pmax, base)
+        assert (tab.cpu() - O.pos_embed_cropped(E, h, w, pmax, base)).abs().max().item() < 1e-6
+
+
+def test_patch_embed(sd3):
+    torch.manual_seed(9)
+    lat = torch.randn(2, 16, 8, 12, device="cuda").bfloat16().float()
+    w = (torch.randn(64, 16, 2, 2, device="cuda") * 0.1).bfloat16()
+    b = torch.randn(64, device="cuda")
+    pt = sd3.pos_embed_table(4, 6, 64, 16, 8)
+    o = sd3.patch_embed(lat, w.view(64, 64).contiguous(), b, pt, 2, 64)
+    ref = torch.nn.functional.conv2d(lat, w.float(), b, stride=2).flatten(2).transpose(1, 2) + pt
+    assert (o.view(2, 24, 64) - ref).abs().max().item() < 1e-4
+
+
+def test_pack_weight_and_cast(sd3):
+    w = torch.randn(70, 33, device="cuda")
+    p = sd3.pack_weight(w, torch.float32)
+    assert torch.equal(p, w.t().contiguous())
+    p16 = sd3.pack_weight(w)
+    assert torch.equal(p16, w.t().contiguous().bfloat16())
+    assert torch.equal(sd3.cast(w, torch.bfloat16), w.bfloat16())
+    assert torch.equal(sd3.cast(w.bfloat16(), torch.float32), w.bfloat16().float())
+
+
+def test_rmsnorm_heads(sd3):
+    torch.manual_seed(10)
+    x = torch.randn(10, 3 * 96, device="cuda")
+    w = torch.randn(32, device="cuda")
+    ref = x.clone().view(10, 9, 32)
+    ref[:, 3:6] = ref[:, 3:6] * torch.rsqrt(ref[:, 3:6].pow(2).mean(-1, keepdim=True) + 1e-6) * w
+    sd3.rmsnorm_heads(x, 96, 3, 32, w, 1e-6)
+    assert (x.view(10, 9, 32) - ref).abs().max().item() < 1e-5
