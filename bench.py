@@ -1,0 +1,509 @@
+"""Benchmark of the SD3.5-medium MMDiT-X denoiser forward on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Metric: denoise steps/s at 1024x1024, batch 8, bf16 (one step = one full
+denoiser forward for a batch of 8 samples: latent 16x128x128 -> 4096 image
+tokens, 333 context tokens x 4096, pooled 2048, 24 blocks, first 13 with the
+extra image-only attention).  Weights are random N(0, 0.02) of the SD3.5-medium
+architecture and inputs are N(0, 1) (seed 2): synthetic stand-ins, no dataset
+or checkpoint is involved.
+
+Each rank runs the whole workload on its own GPU (every GPU holds the full
+weight set, no collective on the data path); `value` is the number of
+batch-8 steps all ranks completed per second, timed with CUDA events, MAX over
+ranks.  Prints ONE JSON line on rank 0.
+
+--impl reference times the reference's CPU implementation of the same path
+(its PyTorch modules, restated in oracle/mmdit_oracle.py) on the host cores,
+on a bounded sample (one of the eight samples of a step).
+"""
+import argparse
+import importlib.util
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+METRIC = "SD3.5-M DiT denoise steps/sec @1024^2 b8 bf16"
+UNIT = "steps/s"
+# algorithmic FLOPs of one step (2MNK per GEMM + 4 T^2 E per attention), batch 8
+STEP_TFLOP = 89.997
+B, TC, HW, TX = 8, 333, 128, 4096
+E, NH, FH = 1536, 24, 6144
+T = TC + TX
+
+
+def load_binding():
+    spec = importlib.util.spec_from_file_location("sd3_b200", os.path.join(REPO, "sd3.c_b200", "sd3_b200.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["sd3_b200"] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def measured_peaks():
+    path = os.path.join(REPO, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"],
+                    bf16_tflops_sustained=d["bf16_tflops_sustained"], source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.QUERY,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ts, line in self.lines:
+            if ts < t0 or ts > t1 + 0.1:
+                continue
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def device_params(torch, O, device, seed):
+    """SD3.5-medium parameters N(0, 0.02), biases 0, generated on the device."""
+    c = O.SD35_MEDIUM
+    shapes = O.model_param_shapes(c["num_layers"], c["dual_layers"], c["in_dim"], c["E"],
+                                  c["pooled_dim"], c["captions_dim"], c["patch"], c["attn_heads"],
+                                  c["mlp_expand"])
+    gen = torch.Generator(device=device).manual_seed(seed)
+    p = {}
+    for name, shp in shapes.items():
+        if len(shp) >= 2:
+            p[name] = (torch.randn(shp, generator=gen, device=device) * 0.02).to(torch.bfloat16)
+        elif "rmsnorm" in name:
+            p[name] = torch.ones(shp, device=device, dtype=torch.bfloat16)
+        else:
+            p[name] = torch.zeros(shp, device=device, dtype=torch.bfloat16)
+    return p
+
+
+def time_events(torch, fn, iters, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def kernel_breakdown(torch, s, peaks):
+    """Times the hot kernels alone at the workload's shapes (CUDA events on the
+    launching stream, inputs larger than L2) and relates them to the peaks."""
+    dev = "cuda"
+    out = []
+    tf_peak = peaks["bf16_tflops"]
+
+    def gemm_case(name, M, N, K, count, kind="plain"):
+        x = torch.randn(M, K, device=dev).bfloat16()
+        w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+        bias = torch.zeros(N, device=dev)
+        if kind == "gate":
+            gate = torch.randn(B, N, device=dev)
+            resid = torch.zeros(M, N, device=dev)
+            fn = lambda: s.check(s.lib().sd3_linear_gate_residual(
+                s.ptr(x), s.ptr(w), s.ptr(bias), s.ptr(gate), N, M // B, s.ptr(resid), M, N, K, s.stream_ptr()))
+        elif kind == "qkv":
+            wq = torch.ones(64, device=dev)
+            qkv = torch.empty(B, M // B, N, device=dev, dtype=torch.bfloat16)
+            fn = lambda: s.qkv_project(x, w, bias, wq, wq, 1e-6, qkv, B, M // B, M // B, 0, K)
+        else:
+            o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            act = 1 if kind == "gelu" else 0
+            fn = lambda: s.check(s.lib().sd3_linear(s.ptr(x), s.ptr(w), s.ptr(bias), s.ptr(o), 1, M, N, K, act, s.stream_ptr()))
+        ms = time_events(torch, fn, 10)
+        fl = 2.0 * M * N * K
+        out.append(dict(kernel=name, launches_per_step=count, ms=round(ms, 4),
+                        achieved=round(fl / ms / 1e9, 1), unit="TFLOP/s", bound="tensor",
+                        frac=round(fl / ms / 1e9 / tf_peak, 4)))
+
+    Mx = B * TX
+    gemm_case("gemm_tcgen05 qkv x (QK-RMSNorm epilogue)", Mx, 3 * E, E, 37, "qkv")
+    gemm_case("gemm_tcgen05 out-proj x (gate+residual)", Mx, E, E, 37, "gate")
+    gemm_case("gemm_tcgen05 mlp1 x (GELU-tanh)", Mx, FH, E, 24, "gelu")
+    gemm_case("gemm_tcgen05 mlp2 x (gate+residual)", Mx, E, FH, 24, "gate")
+
+    def attn_case(name, Tn, Tc, count):
+        qkv = torch.randn(B, Tn, 3 * E, device=dev).bfloat16()
+        oc = torch.empty(B, max(Tc, 1), E, device=dev, dtype=torch.bfloat16)
+        ox = torch.empty(B, Tn - Tc, E, device=dev, dtype=torch.bfloat16)
+        fn = lambda: s.check(s.lib().sd3_attention(s.ptr(qkv), B, Tn, NH, Tc, s.ptr(oc) if Tc else None,
+                                                   s.ptr(ox), 0.125, s.stream_ptr()))
+        ms = time_events(torch, fn, 5)
+        fl = 4.0 * B * NH * Tn * Tn * 64
+        d = dict(kernel=name, launches_per_step=count, ms=round(ms, 4), achieved=round(fl / ms / 1e9, 1),
+                 unit="TFLOP/s", bound="tensor", frac=round(fl / ms / 1e9 / tf_peak, 4))
+        out.append(d)
+        return d
+
+    joint = attn_case("attention_tcgen05 joint T=4429", T, TC, 24)
+    attn_case("attention_tcgen05 image-only T=4096", TX, 0, 13)
+
+    x = torch.randn(Mx, E, device=dev)
+    mod = torch.randn(B, 9 * E, device=dev)
+    o1 = torch.empty(Mx, E, device=dev, dtype=torch.bfloat16)
+    fn = lambda: s.check(s.lib().sd3_layernorm_modulate(s.ptr(x), B, TX, E, 1e-6, mod.data_ptr(), mod[:, E:].data_ptr(),
+                                                        s.ptr(o1), None, None, None, 9 * E, 1, s.stream_ptr()))
+    ms = time_events(torch, fn, 10)
+    by = Mx * E * 6.0
+    out.append(dict(kernel="ln_modulate x (fp32 in, bf16 out)", launches_per_step=61, ms=round(ms, 4),
+                    achieved=round(by / ms / 1e6, 1), unit="GB/s", bound="hbm",
+                    frac=round(by / ms / 1e6 / peaks["hbm_gbs"], 4)))
+    N = 499200
+    y = torch.randn(B, E, device=dev)
+    w = (torch.randn(N, E, device=dev) * 0.02).bfloat16()
+    bb = torch.zeros(N, device=dev)
+    oo = torch.empty(B, N, device=dev)
+    fn = lambda: s.check(s.lib().sd3_skinny_linear(s.ptr(y), E, s.ptr(w), 1, s.ptr(bb), None, 0, s.ptr(oo), N, B, N, E, 0, s.stream_ptr()))
+    ms = time_events(torch, fn, 10)
+    by = N * E * 2.0
+    out.append(dict(kernel="skinny_linear AdaLN (all blocks)", launches_per_step=1, ms=round(ms, 4),
+                    achieved=round(by / ms / 1e6, 1), unit="GB/s", bound="hbm",
+                    frac=round(by / ms / 1e6 / peaks["hbm_gbs"], 4)))
+    return out, joint
+
+
+def profile_case(name, reps=3):
+    """Runs ONE hot kernel a few times at a reduced size (inputs above L2, well
+    under 2 GB) so that a profiler capture of it ends quickly.  Cases:
+    gemm_plain, gemm_qkv, gemm_gate, gemm_gelu, attn_joint, attn_self, ln_mod, skinny."""
+    import torch
+    s = load_binding()
+    dev = "cuda"
+    torch.manual_seed(0)
+    Bp = 2
+    M = Bp * TX
+    if name.startswith("gemm"):
+        N, K = {"gemm_plain": (3 * E, E), "gemm_qkv": (3 * E, E), "gemm_gate": (E, FH), "gemm_gelu": (FH, E)}[name]
+        x = torch.randn(M, K, device=dev).bfloat16()
+        w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+        bias = torch.zeros(N, device=dev)
+        if name == "gemm_gate":
+            gate = torch.randn(Bp, N, device=dev)
+            resid = torch.zeros(M, N, device=dev)
+            fn = lambda: s.check(s.lib().sd3_linear_gate_residual(
+                s.ptr(x), s.ptr(w), s.ptr(bias), s.ptr(gate), N, TX, s.ptr(resid), M, N, K, s.stream_ptr()))
+        elif name == "gemm_qkv":
+            wq = torch.ones(64, device=dev)
+            qkv = torch.empty(Bp, TX, N, device=dev, dtype=torch.bfloat16)
+            fn = lambda: s.qkv_project(x, w, bias, wq, wq, 1e-6, qkv, Bp, TX, TX, 0, K)
+        else:
+            o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            act = 1 if name == "gemm_gelu" else 0
+            fn = lambda: s.check(s.lib().sd3_linear(s.ptr(x), s.ptr(w), s.ptr(bias), s.ptr(o), 1, M, N, K, act, s.stream_ptr()))
+    elif name in ("attn_joint", "attn_self"):
+        Tn, Tc = (T, TC) if name == "attn_joint" else (TX, 0)
+        qkv = torch.randn(Bp, Tn, 3 * E, device=dev).bfloat16()
+        oc = torch.empty(Bp, max(Tc, 1), E, device=dev, dtype=torch.bfloat16)
+        ox = torch.empty(Bp, Tn - Tc, E, device=dev, dtype=torch.bfloat16)
+        fn = lambda: s.check(s.lib().sd3_attention(s.ptr(qkv), Bp, Tn, NH, Tc, s.ptr(oc) if Tc else None,
+                                                   s.ptr(ox), 0.125, s.stream_ptr()))
+    elif name == "ln_mod":
+        Bl = 8
+        x = torch.randn(Bl * TX, E, device=dev)
+        mod = torch.randn(Bl, 9 * E, device=dev)
+        o1 = torch.empty(Bl * TX, E, device=dev, dtype=torch.bfloat16)
+        fn = lambda: s.check(s.lib().sd3_layernorm_modulate(s.ptr(x), Bl, TX, E, 1e-6, mod.data_ptr(), mod[:, E:].data_ptr(),
+                                                            s.ptr(o1), None, None, None, 9 * E, 1, s.stream_ptr()))
+    elif name == "skinny":
+        N = 499200
+        y = torch.randn(B, E, device=dev)
+        w = (torch.randn(N, E, device=dev) * 0.02).bfloat16()
+        bb = torch.zeros(N, device=dev)
+        oo = torch.empty(B, N, device=dev)
+        fn = lambda: s.check(s.lib().sd3_skinny_linear(s.ptr(y), E, s.ptr(w), 1, s.ptr(bb), None, 0, s.ptr(oo), N, B, N, E, 0, s.stream_ptr()))
+    else:
+        raise SystemExit("unknown profile case " + name)
+    ms = time_events(torch, fn, reps, warm=1)
+    s.assert_healthy()
+    print(json.dumps({"profile_case": name, "ms": ms}))
+
+
+def cpu_baseline_sample(torch, O, params_cpu_bf16, threads):
+    """One forward of ONE sample (1/8 of a step) through the CPU oracle in bf16
+    on the host cores; returns seconds."""
+    torch.set_num_threads(threads)
+    gen = torch.Generator().manual_seed(2)
+    latent = torch.randn(1, 16, HW, HW, generator=gen).bfloat16()
+    captions = torch.randn(1, TC, 4096, generator=gen).bfloat16()
+    pooled = torch.randn(1, 2048, generator=gen).bfloat16()
+    t = torch.rand(1, generator=gen) * 1000
+    with torch.no_grad():
+        t0 = time.time()
+        O.dit_forward(pooled, captions, latent, t, params_cpu_bf16, 24, range(13), 24, 2, 384, 128, True)
+        return time.time() - t0
+
+
+def run_reference(args):
+    """Reference arm: the reference's CPU path (PyTorch modules, restated in the
+    oracle) on all host threads; each step is one sample of the batch of 8."""
+    import torch
+    from oracle import mmdit_oracle as O
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    c = O.SD35_MEDIUM
+    shapes = O.model_param_shapes(c["num_layers"], c["dual_layers"], c["in_dim"], c["E"], c["pooled_dim"],
+                                  c["captions_dim"], c["patch"], c["attn_heads"], c["mlp_expand"])
+    gen = torch.Generator().manual_seed(2)
+    p = {}
+    for name, shp in shapes.items():
+        if len(shp) >= 2:
+            p[name] = torch.empty(shp, dtype=torch.bfloat16).normal_(0, 0.02, generator=gen)
+        elif "rmsnorm" in name:
+            p[name] = torch.ones(shp, dtype=torch.bfloat16)
+        else:
+            p[name] = torch.zeros(shp, dtype=torch.bfloat16)
+    for _ in range(args.warmup):
+        cpu_baseline_sample(torch, O, p, threads)
+    secs = [cpu_baseline_sample(torch, O, p, threads) for _ in range(args.steps)]
+    per_sample = sum(secs) / len(secs)
+    value = 1.0 / (per_sample * B)
+    sample = "one of the 8 samples of a step (B=1, 1024^2, bf16) per timed step; step time = 8 x sample time"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_sample * B * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": {"workload": "SD3.5-medium DiT forward, 1024^2, batch 8, bf16 (CPU, sampled)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-breakdown", action="store_true")
+    ap.add_argument("--profile-case", default=None,
+                    help="run one hot kernel a few times at a reduced size (for profiler captures)")
+    args = ap.parse_args()
+    if args.profile_case:
+        return profile_case(args.profile_case)
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    from oracle import mmdit_oracle as O  # parameter shapes + CPU baseline leg only
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the denoiser has no CPU path")
+    s = load_binding()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    peaks = measured_peaks()
+
+    params = device_params(torch, O, dev, seed=2)
+    model = s.Model(24, range(13), 2048, 4096, 16, E, NH, 4, 2, 384, 128, True, s.PRECISION_BF16)
+    model.load(params)
+    model.reserve(B, TC, HW, HW)
+    gen = torch.Generator(device=dev).manual_seed(2 + rank)
+    latent = torch.randn(B, 16, HW, HW, generator=gen, device=dev).bfloat16()
+    captions = torch.randn(B, TC, 4096, generator=gen, device=dev).bfloat16()
+    pooled = torch.randn(B, 2048, generator=gen, device=dev).bfloat16()
+    tsteps = torch.rand(B, generator=gen, device=dev) * 1000
+    out = torch.empty_like(latent)
+
+    def step():
+        model.forward(pooled, captions, latent, tsteps, out)
+
+    # ---- device-resident timing -------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    s.assert_healthy()
+    if dist:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    torch.cuda.synchronize()
+    s.lib().sd3_launch_count(1)
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    t_wall0 = time.time()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    t_wall1 = time.time()
+    launches = s.lib().sd3_launch_count(0)
+    ms = e0.elapsed_time(e1)
+    if dist:
+        tms = torch.tensor([ms], device=dev)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms = tms.item()
+        dist.barrier()
+    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
+    s.assert_healthy()
+    ms_per_step = ms / args.steps
+    value = world * 1000.0 / ms_per_step
+
+    # ---- end to end: host buffers in, host buffer out, through the same call ----
+    h_lat = latent.cpu().pin_memory()
+    h_cap = captions.cpu().pin_memory()
+    h_pool = pooled.cpu().pin_memory()
+    h_t = tsteps.cpu().pin_memory()
+    h_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+
+    def e2e_step():
+        latent.copy_(h_lat, non_blocking=True)
+        captions.copy_(h_cap, non_blocking=True)
+        pooled.copy_(h_pool, non_blocking=True)
+        tsteps.copy_(h_t, non_blocking=True)
+        model.forward(pooled, captions, latent, tsteps, out)
+        h_out.copy_(out, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms2 = e0.elapsed_time(e1)
+    if dist:
+        tms = torch.tensor([ms2], device=dev)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms2 = tms.item()
+        dist.barrier()
+    e2e_value = world * 1000.0 * args.steps / ms2
+    h2d = sum(t.numel() * t.element_size() for t in (h_lat, h_cap, h_pool, h_t))
+    d2h = h_out.numel() * h_out.element_size()
+
+    if rank != 0:
+        if dist:
+            dist.destroy_process_group()
+        return
+
+    # ---- per-kernel roofline (rank 0, kernels timed alone) -----------------------
+    step_tf = STEP_TFLOP / (ms_per_step / 1e3)
+    kernels, joint = (None, None)
+    if not args.no_breakdown:
+        model.close()
+        del params
+        torch.cuda.empty_cache()
+        kernels, joint = kernel_breakdown(torch, s, peaks)
+    if joint is not None:
+        roofline = {"bound": "tensor", "kernel": "attention_tcgen05_kernel (joint, T=4429, B=8, 24 heads)",
+                    "achieved": joint["achieved"], "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                    "frac": joint["frac"], "traffic": None, "peak_source": peaks["source"] + " burst"}
+    else:
+        roofline = {"bound": "tensor", "kernel": "whole step", "achieved": round(step_tf, 1),
+                    "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                    "frac": round(step_tf / peaks["bf16_tflops_sustained"], 4), "traffic": None,
+                    "peak_source": peaks["source"] + " sustained"}
+
+    # ---- CPU baseline (rank 0, N=1 only): bounded sample on the host cores -------
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        pcpu = {k: v.cpu() for k, v in device_params(torch, O, dev, seed=2).items()}
+        torch.cuda.empty_cache()
+        secs = cpu_baseline_sample(torch, O, pcpu, threads)
+        cpu = {"value": 1.0 / (secs * B), "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": "one forward of 1 of the 8 samples (B=1, 1024^2, bf16) through the CPU oracle; "
+                         "step time = 8 x %.2f s" % secs}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "SD3.5-medium DiT forward (BASELINE config 3): 1024^2, batch 8 per GPU, bf16, "
+                               "4096 image + 333 context tokens, 24 blocks (13 dual)",
+                   "per_gpu_batch": B, "l2": "inputs and activations exceed L2 (126 MB) many times per step"},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "step_tflops": round(step_tf, 1),
+        "step_frac_of_sustained_peak": round(step_tf / peaks["bf16_tflops_sustained"], 4),
+        "step_frac_of_nominal_2250": round(step_tf / 2250.0, 4),
+        "roofline": roofline,
+        "cpu_baseline": cpu,
+        "kernels": kernels,
+    }
+    print(json.dumps(line))
+    if dist:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -90,3 +90,45 @@ def test_sd35_medium_parameter_count():
             k *= d
         n += k
     assert n == 2243171520
+
+
+def _load_reference_cpu_extension():
+    """oracle/_ref/custom_modules_ref.so: the reference's own modules.cpp compiled
+    CPU-only by oracle/build_ref.py (present when a reference checkout was
+    available at build time)."""
+    import importlib.util
+    path = os.path.join(REPO, "oracle", "_ref", "custom_modules_ref.so")
+    if not os.path.exists(path):
+        return None
+    spec = importlib.util.spec_from_file_location("custom_modules_ref", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_oracle_matches_reference_cpp_extension():
+    ref = _load_reference_cpu_extension()
+    if ref is None:
+        pytest.skip("oracle/_ref not built (no reference checkout at build time)")
+    g = golden("model_toy.pt")
+    cfg = g["config"]
+    p = f32(g["params"])
+    out_ref = ref.DiT(g["pooled"].float(), g["captions"].float(), g["latent"].float(), g["timesteps"],
+                      {k: v.clone() for k, v in p.items()}, cfg["num_layers"],
+                      set(cfg["dual_attention_layers"]), cfg["pooled_dim"], cfg["captions_dim"],
+                      cfg["in_channels"], cfg["emb_dim"], cfg["attn_heads"], cfg["mlp_expand"],
+                      cfg["patch_size"], cfg["pos_embed_max_size"], cfg["base_height"], True)
+    out = O.dit_forward(g["pooled"].float(), g["captions"].float(), g["latent"].float(), g["timesteps"],
+                        p, cfg["num_layers"], cfg["dual_attention_layers"], cfg["attn_heads"],
+                        cfg["patch_size"], cfg["pos_embed_max_size"], cfg["base_height"], True)
+    assert (out - out_ref).abs().max().item() < 1e-5
+    gb = golden("block_dual.pt")
+    cb = gb["config"]
+    pb = f32(gb["params"])
+    c, x = gb["c"].float().clone(), gb["x"].float().clone()
+    ref.Dit_block(gb["y"].float(), c, x, pb, cb["B"], cb["Tc"], cb["Tx"], cb["emb_dim"], cb["attn_heads"],
+                  cb["mlp_expand"], cb["use_dual_attention"], cb["use_qk_norm"], cb["discard_context"])
+    co, xo = O.dit_block(gb["x"].float(), gb["c"].float(), gb["y"].float(), pb, cb["attn_heads"],
+                         cb["use_dual_attention"], cb["use_qk_norm"], cb["discard_context"])
+    assert (x - xo).abs().max().item() < 1e-5
+    assert (c - co).abs().max().item() < 1e-5
