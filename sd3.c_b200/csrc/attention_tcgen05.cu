@@ -3,14 +3,17 @@
 // context||image attention of every block and the image-only attention of the
 // dual blocks.
 //
-// One CTA owns a 128-query tile of one (sample, head).  Warp 0 streams K and V
-// tiles (128 keys each) with TMA from the packed (B, T, 3E) q|k|v buffer, warp
-// 1 issues S = Q K^T into TMEM, the four softmax warps (one query row per
-// thread, TMEM lane == row) turn S into P = exp2(S c - m c) in place (bf16,
-// packed two per TMEM column, aliasing the S columns), and warp 1 then issues
-// O += P V with P read from TMEM and V from shared memory in MN-major form.
-// The T x T score matrix is never written to memory.  Two CTAs are resident
-// per SM so one CTA's softmax overlaps the other's MMAs.
+// One CTA owns a 128-query tile of one (sample, head); two CTAs are resident
+// per SM.  Warp 0 streams K and V tiles (128 keys per stage) with TMA from the
+// packed (B, T, 3E) q|k|v buffer.  The keys are consumed in sub-tiles of 64:
+// warp 1 issues S_t = Q K_t^T into one of two 64-column TMEM buffers, always
+// one sub-tile ahead of the softmax, so the four softmax warps (one query row
+// per thread, TMEM lane == row) find their scores ready and never wait for the
+// tensor pipe.  They turn S_t into P_t = exp2(S c - m c) in place (bf16, two
+// per TMEM column, over the first 32 columns of the same buffer), and warp 1
+// then issues O += P_t V_t with P read from TMEM and V from shared memory in
+// MN-major form, followed by S_{t+2} into the buffer just freed.  The T x T
+// score matrix never exists in memory.
 //
 // Replaces mha_cuda (cuda/dit.cu:612-652: two cublasSgemmStridedBatched calls
 // around scale_softmax_kernel2, cuda/dit.cu:548-608, over materialised T x T
@@ -31,13 +34,15 @@ int encode_tmap_3d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t 
 namespace {
 
 constexpr int AT_BM = 128;      // queries per CTA
-constexpr int AT_BN = 128;      // keys per tile
+constexpr int AT_BN = 128;      // keys per shared-memory stage
+constexpr int AT_SUB = 64;      // keys per score sub-tile
 constexpr int AT_D = 64;        // head dim
 constexpr int AT_STAGES = 2;    // K/V ring depth
 constexpr int AT_TILE_BYTES = AT_BN * AT_D * 2;  // 16 KiB
+constexpr int AT_SUB_BYTES = AT_SUB * AT_D * 2;  // 8 KiB
 constexpr int AT_THREADS = 192;
 constexpr int AT_TMEM_COLS = 256;
-constexpr int AT_S_COL = 0;     // S: 128 fp32 columns; P (bf16 pairs) reuses columns [0, 64)
+constexpr int AT_S_COL = 0;     // two score buffers of 64 fp32 columns: [0,64) and [64,128)
 constexpr int AT_O_COL = 128;   // O: 64 fp32 columns
 constexpr int AT_SMEM_BYTES = (1 + 2 * AT_STAGES) * AT_TILE_BYTES + 256 + 1024;
 
@@ -54,6 +59,11 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 
 __global__ void __launch_bounds__(AT_THREADS, 2)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
@@ -69,9 +79,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
   uint64_t* v_full = k_full + AT_STAGES;    // AT_STAGES
   uint64_t* k_empty = v_full + AT_STAGES;   // AT_STAGES
   uint64_t* v_empty = k_empty + AT_STAGES;  // AT_STAGES
-  uint64_t* s_full = v_empty + AT_STAGES;   // 1
-  uint64_t* p_ready = s_full + 1;           // 1
-  uint64_t* o_full = p_ready + 1;           // 1
+  uint64_t* s_full = v_empty + AT_STAGES;   // 2 (one per score buffer)
+  uint64_t* p_ready = s_full + 2;           // 2
+  uint64_t* pv_done = p_ready + 2;          // 1: one phase per P V product
+  uint64_t* o_full = pv_done + 1;           // 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
   int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
 
@@ -80,7 +91,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
   const int h = blockIdx.y;
   const int b = blockIdx.z;
   const int T = a.T;
-  const int nkv = (T + AT_BN - 1) / AT_BN;
+  const int nkv = (T + AT_BN - 1) / AT_BN;    // shared-memory stages to stream
+  const int nsub = (T + AT_SUB - 1) / AT_SUB;  // score sub-tiles
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -90,8 +102,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
       mbar_init(&k_empty[s], 1);
       mbar_init(&v_empty[s], 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(p_ready, 4);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_ready[s], 4);
+    }
+    mbar_init(pv_done, 1);
     mbar_init(o_full, 1);
     *s_abort = 0;
     fence_barrier_init();
@@ -133,97 +148,97 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
-    constexpr uint32_t IDESC_S = make_idesc(1, 1, AT_BM, AT_BN, 0, 0);  // Q K^T, both K-major
-    constexpr uint32_t IDESC_O = make_idesc(1, 1, AT_BM, AT_D, 0, 1);   // P V, V is MN-major
-    const uint32_t s_tmem = tmem_base + AT_S_COL;
+    constexpr uint32_t IDESC_S = make_idesc(1, 1, AT_BM, AT_SUB, 0, 0);  // Q K^T, both K-major
+    constexpr uint32_t IDESC_O = make_idesc(1, 1, AT_BM, AT_D, 0, 1);    // P V, V is MN-major
     const uint32_t o_tmem = tmem_base + AT_O_COL;
     const uint64_t q_desc = make_smem_desc_sw128(smem_u32(q_smem), 16, 1024);
-    bool ok = mbar_wait(q_full, 0, wc, DEV_TIMEOUT_ATTN_Q);
-    // S_0
-    if (ok) ok = mbar_wait(&k_full[0], 0, wc, DEV_TIMEOUT_ATTN_KV);
-    if (ok) {
-      tc_fence_after_sync();
+
+    // S_u = Q K_u^T for sub-tile u into score buffer (u & 1); releases the K
+    // stage after its second half (or after the last sub-tile).
+    auto issue_s = [&](int u) -> bool {
+      const int j = u >> 1, st = j % AT_STAGES;
+      if ((u & 1) == 0) {
+        if (!mbar_wait(&k_full[st], (j / AT_STAGES) & 1, wc, DEV_TIMEOUT_ATTN_KV)) return false;
+        tc_fence_after_sync();
+      }
       if (lane == 0) {
-        const uint64_t k_desc = make_smem_desc_sw128(smem_u32(k_smem), 16, 1024);
+        const uint32_t s_tmem = tmem_base + AT_S_COL + (u & 1) * AT_SUB;
+        const uint64_t k_desc = make_smem_desc_sw128(
+            smem_u32(k_smem + st * AT_TILE_BYTES + (u & 1) * AT_SUB_BYTES), 16, 1024);
 #pragma unroll
         for (int k = 0; k < AT_D / 16; ++k)
           mma_f16_ss(s_tmem, q_desc + 2 * k, k_desc + 2 * k, IDESC_S, k != 0);
-        mma_commit(&k_empty[0]);
-        mma_commit(s_full);
+        mma_commit(&s_full[u & 1]);
+        if ((u & 1) == 1 || u == nsub - 1) mma_commit(&k_empty[st]);
       }
       __syncwarp();
-    }
-    for (int j = 0; j < nkv && ok; ++j) {
-      const int st = j % AT_STAGES;
-      const uint32_t ph = (j / AT_STAGES) & 1;
-      // O += P_j V_j
-      if (!mbar_wait(p_ready, j & 1, wc, DEV_TIMEOUT_ATTN_P)) break;
-      if (!mbar_wait(&v_full[st], ph, wc, DEV_TIMEOUT_ATTN_KV)) break;
+      return true;
+    };
+
+    bool ok = mbar_wait(q_full, 0, wc, DEV_TIMEOUT_ATTN_Q);
+    if (ok) ok = issue_s(0);
+    if (ok && nsub > 1) ok = issue_s(1);
+    for (int t = 0; t < nsub && ok; ++t) {
+      const int j = t >> 1, st = j % AT_STAGES;
+      // O += P_t V_t
+      if (!mbar_wait(&p_ready[t & 1], (t >> 1) & 1, wc, DEV_TIMEOUT_ATTN_P)) break;
+      if ((t & 1) == 0) {
+        if (!mbar_wait(&v_full[st], (j / AT_STAGES) & 1, wc, DEV_TIMEOUT_ATTN_KV)) break;
+      }
       tc_fence_after_sync();
       if (lane == 0) {
-        const uint64_t v_desc =
-            make_smem_desc_sw128(smem_u32(v_smem + st * AT_TILE_BYTES), 1024, 1024);
+        const uint32_t p_tmem = tmem_base + AT_S_COL + (t & 1) * AT_SUB;
+        const uint64_t v_desc = make_smem_desc_sw128(
+            smem_u32(v_smem + st * AT_TILE_BYTES + (t & 1) * AT_SUB_BYTES), 1024, 1024);
 #pragma unroll
-        for (int k = 0; k < AT_BN / 16; ++k) {
+        for (int k = 0; k < AT_SUB / 16; ++k) {
           // 16 keys: 8 TMEM columns of packed bf16 pairs; 16 rows of V (128 B each)
-          mma_f16_ts(o_tmem, s_tmem + 8 * k, v_desc + static_cast<uint64_t>((k * 16 * 128) >> 4),
-                     IDESC_O, (j | k) != 0);
+          mma_f16_ts(o_tmem, p_tmem + 8 * k, v_desc + static_cast<uint64_t>((k * 16 * 128) >> 4),
+                     IDESC_O, (t | k) != 0);
         }
-        mma_commit(&v_empty[st]);
-        if (j == nkv - 1) mma_commit(o_full);
+        mma_commit(pv_done);
+        if ((t & 1) == 1 || t == nsub - 1) mma_commit(&v_empty[st]);
+        if (t == nsub - 1) mma_commit(o_full);
       }
       __syncwarp();
-      // S_{j+1}
-      if (j + 1 < nkv) {
-        const int st1 = (j + 1) % AT_STAGES;
-        const uint32_t ph1 = ((j + 1) / AT_STAGES) & 1;
-        if (!mbar_wait(&k_full[st1], ph1, wc, DEV_TIMEOUT_ATTN_KV)) break;
-        tc_fence_after_sync();
-        if (lane == 0) {
-          const uint64_t k_desc =
-              make_smem_desc_sw128(smem_u32(k_smem + st1 * AT_TILE_BYTES), 16, 1024);
-#pragma unroll
-          for (int k = 0; k < AT_D / 16; ++k)
-            mma_f16_ss(s_tmem, q_desc + 2 * k, k_desc + 2 * k, IDESC_S, k != 0);
-          mma_commit(&k_empty[st1]);
-          mma_commit(s_full);
-        }
-        __syncwarp();
-      }
+      // the buffer of P_t is free once that product has been issued (the
+      // tensor pipe executes in issue order): refill it with S_{t+2}
+      if (t + 2 < nsub) ok = issue_s(t + 2);
     }
   } else {
     // ------------------------------ softmax + epilogue ------------------------
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
-    const uint32_t s_tmem = lane_base + AT_S_COL;
     const uint32_t o_tmem = lane_base + AT_O_COL;
     const float c = a.scale_log2e;
     float m_used = -INFINITY;  // running max (raw score units) the exponentials refer to
     float l = 0.f;
     bool ok = true;
-    for (int j = 0; j < nkv; ++j) {
-      if (!mbar_wait(s_full, j & 1, wc, DEV_TIMEOUT_ATTN_S)) { ok = false; break; }
+    for (int t = 0; t < nsub; ++t) {
+      const uint32_t s_tmem = lane_base + AT_S_COL + (t & 1) * AT_SUB;
+      if (!mbar_wait(&s_full[t & 1], (t >> 1) & 1, wc, DEV_TIMEOUT_ATTN_S)) { ok = false; break; }
       tc_fence_after_sync();
-      const int kv0 = j * AT_BN;
-      const bool tail = (kv0 + AT_BN > T);
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(s_tmem + ch * 32, r);
-        tmem_wait_ld();
-        if (tail) {
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32b_x32(s_tmem, r0);
+      tmem_ld_32x32b_x32(s_tmem + 32, r1);
+      tmem_wait_ld();
+      const int kv0 = t * AT_SUB;
+      if (kv0 + AT_SUB > T) {  // ragged last sub-tile: keys >= T do not exist
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (kv0 + ch * 32 + i < T) mx = fmaxf(mx, __uint_as_float(r[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        for (int i = 0; i < 32; ++i) {
+          if (kv0 + i >= T) r0[i] = 0xff800000u;  // -inf
+          if (kv0 + 32 + i >= T) r1[i] = 0xff800000u;
         }
       }
-      if (j == 0) {
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        mx0 = max3(mx0, __uint_as_float(r0[i]), __uint_as_float(r0[i + 1]));
+        mx1 = max3(mx1, __uint_as_float(r1[i]), __uint_as_float(r1[i + 1]));
+      }
+      const float mx = fmaxf(mx0, mx1);
+      if (t == 0) {
         m_used = mx;
       } else {
         // Rescale O only when the maximum moved by more than 2^8 in the exp2
@@ -236,46 +251,44 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
             m_used = mx;
             l *= alpha;
           }
-          uint32_t o0[32], o1[32];
+          // P_{t-1} V_{t-1} must have landed in O before O is rescaled; the
+          // product of this sub-tile is only issued after p_ready below.
+          if (!mbar_wait(pv_done, (t - 1) & 1, wc, DEV_TIMEOUT_ATTN_O)) { ok = false; break; }
+          tc_fence_after_sync();
+          uint32_t o0[32];
           tmem_ld_32x32b_x32(o_tmem, o0);
-          tmem_ld_32x32b_x32(o_tmem + 32, o1);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            o0[i] = __float_as_uint(__uint_as_float(o0[i]) * alpha);
-            o1[i] = __float_as_uint(__uint_as_float(o1[i]) * alpha);
-          }
+          for (int i = 0; i < 32; ++i) o0[i] = __float_as_uint(__uint_as_float(o0[i]) * alpha);
           tmem_st_32x32b_x32(o_tmem, o0);
-          tmem_st_32x32b_x32(o_tmem + 32, o1);
+          tmem_ld_32x32b_x32(o_tmem + 32, o0);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o0[i] = __float_as_uint(__uint_as_float(o0[i]) * alpha);
+          tmem_st_32x32b_x32(o_tmem + 32, o0);
         }
       }
       const float mc = m_used * c;
-      // pass 2: P = exp2(S c - m c), packed to bf16 pairs over the S columns
-      float lsum = 0.f;
-#pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(s_tmem + ch * 32, r);
-        tmem_wait_ld();
-        uint32_t pk[16];
+      // P = exp2(S c - m c), packed to bf16 pairs over the first 32 columns of the buffer
+      float ls0 = 0.f, ls1 = 0.f;
+      uint32_t pk[32];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float p0 = ex2_approx(fmaf(__uint_as_float(r[2 * i]), c, -mc));
-          float p1 = ex2_approx(fmaf(__uint_as_float(r[2 * i + 1]), c, -mc));
-          if (tail) {
-            if (kv0 + ch * 32 + 2 * i >= T) p0 = 0.f;
-            if (kv0 + ch * 32 + 2 * i + 1 >= T) p1 = 0.f;
-          }
-          lsum += p0 + p1;
-          pk[i] = pack_bf16x2(p0, p1);
-        }
-        tmem_st_32x32b_x16(s_tmem + ch * 16, pk);
+      for (int i = 0; i < 16; ++i) {
+        const float p0 = ex2_approx(fmaf(__uint_as_float(r0[2 * i]), c, -mc));
+        const float p1 = ex2_approx(fmaf(__uint_as_float(r0[2 * i + 1]), c, -mc));
+        const float p2 = ex2_approx(fmaf(__uint_as_float(r1[2 * i]), c, -mc));
+        const float p3 = ex2_approx(fmaf(__uint_as_float(r1[2 * i + 1]), c, -mc));
+        ls0 += p0 + p1;
+        ls1 += p2 + p3;
+        pk[i] = pack_bf16x2(p0, p1);
+        pk[16 + i] = pack_bf16x2(p2, p3);
       }
-      l += lsum;
+      tmem_st_32x32b_x32(s_tmem, pk);
+      l += ls0 + ls1;
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_ready);
+      if (lane == 0) mbar_arrive(&p_ready[t & 1]);
     }
     if (ok && mbar_wait(o_full, 0, wc, DEV_TIMEOUT_ATTN_O)) {
       tc_fence_after_sync();

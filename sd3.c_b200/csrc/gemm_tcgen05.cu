@@ -29,7 +29,8 @@ namespace {
 constexpr int BM = 128;
 constexpr int STAGE_K_BYTES = 128;  // bytes of K per smem row == swizzle span
 constexpr int A_STAGE_BYTES = BM * STAGE_K_BYTES;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
+constexpr int EPI_WARPS = 8;
 
 template <int BN>
 struct GemmCfg {
@@ -49,9 +50,11 @@ struct GemmArgs {
 };
 
 __device__ __forceinline__ float gelu_tanh_f(float x) {
-  // 0.5 x (1 + tanh(u)) == x * sigmoid(2u),  u = sqrt(2/pi) (x + 0.044715 x^3)
+  // 0.5 x (1 + tanh(u)),  u = sqrt(2/pi) (x + 0.044715 x^3); one MUFU op per element
   const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  return x * __frcp_rn(1.0f + __expf(-2.0f * u));
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  return 0.5f * x * (1.0f + t);
 }
 
 template <bool OUT_F32>
@@ -176,6 +179,41 @@ __device__ __forceinline__ void epilogue_64(float (&v)[64], int m, int n_base,
   }
 }
 
+// Residual row segment of 32 columns into registers (issued early so that the
+// DRAM/L2 latency overlaps the main loop or the previous sub-chunk).
+__device__ __forceinline__ void load_resid32(const float* p, int n_base, int N, float4 (&rr)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    if (n_base + i * 4 < N) {
+      asm volatile("ld.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+                   : "=f"(rr[i].x), "=f"(rr[i].y), "=f"(rr[i].z), "=f"(rr[i].w)
+                   : "l"(p + i * 4));
+    }
+  }
+}
+
+// out = resid + gate[b] * (acc * alpha + bias) on 32 columns of one row
+__device__ __forceinline__ void epilogue_gate32(const uint32_t (&acc)[32], const float4 (&rr)[8],
+                                                float* out_row, const float* gate_row, int n_base,
+                                                const GemmArgs& g) {
+  const GemmEpilogue& e = g.epi;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int n = n_base + i * 4;
+    if (n < g.N) {
+      const float4 gg = __ldg(reinterpret_cast<const float4*>(gate_row + n));
+      float4 bb = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (e.bias) bb = __ldg(reinterpret_cast<const float4*>(e.bias + n));
+      float4 o;
+      o.x = fmaf(gg.x, fmaf(__uint_as_float(acc[4 * i + 0]), e.alpha, bb.x), rr[i].x);
+      o.y = fmaf(gg.y, fmaf(__uint_as_float(acc[4 * i + 1]), e.alpha, bb.y), rr[i].y);
+      o.z = fmaf(gg.z, fmaf(__uint_as_float(acc[4 * i + 2]), e.alpha, bb.z), rr[i].z);
+      o.w = fmaf(gg.w, fmaf(__uint_as_float(acc[4 * i + 3]), e.alpha, bb.w), rr[i].w);
+      *reinterpret_cast<float4*>(out_row + n) = o;
+    }
+  }
+}
+
 template <int BN, int EPI, bool OUT_F32, bool FP8>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
@@ -207,7 +245,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 4);
+      mbar_init(&tempty_bar[a], EPI_WARPS);
     }
     *s_abort = 0;
     fence_barrier_init();
@@ -285,34 +323,74 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else {
     // ------------------------------ epilogue ----------------------------------
-    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    // Eight warps: warp w may read TMEM lanes [32 (w % 4), +32); warps 2-5 take
+    // the first half of the tile's columns, warps 6-9 the second half.
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
+    constexpr int COLS_PER_WARP = BN / 2;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int m0 = (tile / g.tiles_n) * BM;
       const int n0 = (tile % g.tiles_n) * BN;
-      if (!mbar_wait(&tfull_bar[acc], acc_phase, wc, DEV_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-      tc_fence_after_sync();
       const int m = m0 + row;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                              static_cast<uint32_t>(acc * BN);
-#pragma unroll 1
-      for (int c = 0; c < BN / 64; ++c) {
-        const int n_base = n0 + c * 64;
-        if (n_base >= g.N) break;  // warp-uniform
-        uint32_t r0[32], r1[32];
-        tmem_ld_32x32b_x32(t_row + c * 64, r0);
-        tmem_ld_32x32b_x32(t_row + c * 64 + 32, r1);
-        tmem_wait_ld();
-        float v[64];
+      if constexpr (EPI == EPI_GATE_RESID) {
+        // 32 columns at a time; the residual of sub-chunk i+1 is requested
+        // before sub-chunk i is processed, the first one before the accumulator
+        // is even complete.
+        constexpr int NSUB = COLS_PER_WARP / 32;
+        const GemmEpilogue& e = g.epi;
+        const bool valid = m < g.M;
+        const int mm = valid ? m : 0;
+        const int b = mm / e.rows_in;
+        float* out_row = static_cast<float*>(e.out) + static_cast<long>(mm) * e.ldo;
+        const float* res_row = e.resid + static_cast<long>(mm) * e.ldo;
+        const float* gate_row = e.gate + static_cast<long>(b) * e.gate_stride;
+        const int nw = n0 + half * COLS_PER_WARP;
+        float4 rr[8], rn[8];
+        if (valid) load_resid32(res_row + nw, nw, g.N, rr);
+        if (!mbar_wait(&tfull_bar[acc], acc_phase, wc, DEV_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after_sync();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          v[j] = __uint_as_float(r0[j]);
-          v[32 + j] = __uint_as_float(r1[j]);
+        for (int sub = 0; sub < NSUB; ++sub) {
+          const int n_base = nw + sub * 32;
+          if (sub + 1 < NSUB && valid) load_resid32(res_row + n_base + 32, n_base + 32, g.N, rn);
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_row + half * COLS_PER_WARP + sub * 32, r);
+          tmem_wait_ld();
+          if (valid && n_base < g.N) epilogue_gate32(r, rr, out_row, gate_row, n_base, g);
+          if (sub + 1 < NSUB) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) rr[i] = rn[i];
+          }
         }
-        if (m < g.M) epilogue_64<EPI, OUT_F32>(v, m, n_base, g);
+      } else {
+        if (!mbar_wait(&tfull_bar[acc], acc_phase, wc, DEV_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after_sync();
+        constexpr int CHUNKS = COLS_PER_WARP >= 64 ? COLS_PER_WARP / 64 : 1;
+        const bool active = COLS_PER_WARP >= 64 || half == 0;  // BN = 64: one chunk, first half only
+        const int c_first = COLS_PER_WARP >= 64 ? half * CHUNKS : 0;
+#pragma unroll 1
+        for (int ci = 0; ci < CHUNKS; ++ci) {
+          const int c = c_first + ci;
+          const int n_base = n0 + c * 64;
+          if (!active || n_base >= g.N) break;  // warp-uniform
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32b_x32(t_row + c * 64, r0);
+          tmem_ld_32x32b_x32(t_row + c * 64 + 32, r1);
+          tmem_wait_ld();
+          float v[64];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = __uint_as_float(r0[j]);
+            v[32 + j] = __uint_as_float(r1[j]);
+          }
+          if (m < g.M) epilogue_64<EPI, OUT_F32>(v, m, n_base, g);
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -493,6 +571,12 @@ int launch_gemm(const void* A, long lda, const void* W, long ldw, int operand_dt
   }
   if (epi.mode == EPI_GATE_RESID && (!epi.gate || !epi.resid)) {
     set_last_error("gemm: gate/residual epilogue needs gate and resid pointers");
+    return ST_INVALID_ARG;
+  }
+  if (epi.mode == EPI_GATE_RESID &&
+      (epi.rows_in <= 0 || epi.rows_in != epi.rows_out || epi.row_off != 0 || epi.ldo % 4 != 0 ||
+       epi.gate_stride % 4 != 0)) {
+    set_last_error("gemm: gate/residual epilogue needs rows_in == rows_out > 0 and no row offset");
     return ST_INVALID_ARG;
   }
   if (epi.mode == EPI_ADD_TABLE && (!epi.table || epi.rows_in <= 0)) {

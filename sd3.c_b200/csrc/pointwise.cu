@@ -145,7 +145,39 @@ __device__ __forceinline__ void load_w8(const float* p, float (&w)[8]) {
   w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
 }
 
-template <typename WT, int R, int BC>
+// raw 8-element weight chunk kept in registers until it is needed
+template <typename WT> struct WChunk;
+template <> struct WChunk<bf16> {
+  uint4 u;
+  __device__ __forceinline__ void load(const bf16* p) { u = __ldg(reinterpret_cast<const uint4*>(p)); }
+  __device__ __forceinline__ void zero() { u = make_uint4(0, 0, 0, 0); }
+  __device__ __forceinline__ void get(float (&w)[8]) const {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(h[j]);
+      w[2 * j] = f.x;
+      w[2 * j + 1] = f.y;
+    }
+  }
+};
+template <> struct WChunk<float> {
+  float4 a, b;
+  __device__ __forceinline__ void load(const float* p) {
+    a = __ldg(reinterpret_cast<const float4*>(p));
+    b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  }
+  __device__ __forceinline__ void zero() { a = b = make_float4(0.f, 0.f, 0.f, 0.f); }
+  __device__ __forceinline__ void get(float (&w)[8]) const {
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+    w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+  }
+};
+
+// Each warp owns R output columns and walks K in slabs of KU * 256 elements;
+// all weight loads of a slab are issued before any of them is consumed, so a
+// warp keeps R * KU * 512 bytes of weight reads in flight.
+template <typename WT, int R, int BC, int KU>
 __global__ void __launch_bounds__(256)
 skinny_linear_kernel(const float* __restrict__ in, long ld_in, const WT* __restrict__ W,
                      const float* __restrict__ bias, const float* __restrict__ add, long ld_add,
@@ -159,26 +191,35 @@ skinny_linear_kernel(const float* __restrict__ in, long ld_in, const WT* __restr
     for (int r = 0; r < R; ++r)
 #pragma unroll
       for (int b = 0; b < BC; ++b) acc[r][b] = 0.f;
-    for (int k = lane * 8; k < K; k += 256) {
-      float w[R][8];
+    for (int kb = 0; kb < K; kb += 256 * KU) {
+      WChunk<WT> wc[R][KU];
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        if (n0 + r < N) {
-          load_w8(W + (n0 + r) * static_cast<long>(K) + k, w[r]);
-        } else {
+      for (int u = 0; u < KU; ++u) {
+        const int k = kb + u * 256 + lane * 8;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) w[r][j] = 0.f;
+        for (int r = 0; r < R; ++r) {
+          if (k < K && n0 + r < N) wc[r][u].load(W + (n0 + r) * static_cast<long>(K) + k);
+          else wc[r][u].zero();
         }
       }
 #pragma unroll
-      for (int b = 0; b < BC; ++b) {
-        if (b0 + b < B) {
-          float xv[8];
-          load_w8(in + (b0 + b) * ld_in + k, xv);
+      for (int u = 0; u < KU; ++u) {
+        const int k = kb + u * 256 + lane * 8;
+        if (k < K) {
+          float w[R][8];
 #pragma unroll
-          for (int r = 0; r < R; ++r) {
+          for (int r = 0; r < R; ++r) wc[r][u].get(w[r]);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[r][b] = fmaf(xv[j], w[r][j], acc[r][b]);
+          for (int b = 0; b < BC; ++b) {
+            if (b0 + b < B) {
+              float xv[8];
+              load_w8(in + (b0 + b) * ld_in + k, xv);
+#pragma unroll
+              for (int r = 0; r < R; ++r) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[r][b] = fmaf(xv[j], w[r][j], acc[r][b]);
+              }
+            }
           }
         }
       }
@@ -340,14 +381,14 @@ int launch_skinny_linear(const float* in, long ld_in, const void* W, int w_f32, 
     set_last_error("skinny_linear: invalid argument (K %d must be a multiple of 8)", K);
     return ST_INVALID_ARG;
   }
-  constexpr int R = 4, BC = 8, WPB = 8;
+  constexpr int R = 2, BC = 8, WPB = 8;
   const long warps = (static_cast<long>(N) + R - 1) / R;
   const unsigned grid = static_cast<unsigned>((warps + WPB - 1) / WPB);
   if (w_f32)
-    skinny_linear_kernel<float, R, BC><<<grid, WPB * 32, 0, stream>>>(
+    skinny_linear_kernel<float, R, BC, 3><<<grid, WPB * 32, 0, stream>>>(
         in, ld_in, static_cast<const float*>(W), bias, add, ld_add, out, ld_out, B, N, K, act_out);
   else
-    skinny_linear_kernel<bf16, R, BC><<<grid, WPB * 32, 0, stream>>>(
+    skinny_linear_kernel<bf16, R, BC, 6><<<grid, WPB * 32, 0, stream>>>(
         in, ld_in, static_cast<const bf16*>(W), bias, add, ld_add, out, ld_out, B, N, K, act_out);
   return after_launch("skinny_linear_kernel");
 }
