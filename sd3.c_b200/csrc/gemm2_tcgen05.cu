@@ -1,0 +1,255 @@
+// CTA-pair variant of the tcgen05 GEMM: two CTAs (a cluster of two on
+// neighbouring SMs) cooperate on 256 x 256 output tiles with
+// tcgen05.mma.cta_group::2.
+//
+//   acc[m, n] = sum_k A[m, k] * W[n, k]        A: (M, K) K-major, W: (N, K) K-major
+//
+// Per 64-wide K block each CTA loads only its own 128 rows of A and its own
+// 128-row half of the W tile (32 KiB instead of the 48 KiB a lone CTA needs
+// for a 128 x 256 tile); the tensor cores of both SMs read the two W halves
+// from both shared memories.  That cuts the L2 -> shared-memory traffic per
+// FLOP by a third and leaves room for a six-stage ring.  The even CTA of the
+// pair issues all MMAs; completion is signalled to both CTAs with
+// tcgen05.commit ... multicast::cluster.  Each CTA keeps the accumulator rows
+// of its own half of M in its own TMEM (two buffers of 256 columns) and drains
+// them through the same fused epilogues as the one-CTA kernel.
+//
+// Loads are plain tiled TMA (cta_group::2 form so the peer's transaction bytes
+// can be credited to the leader's barrier); nothing here is a multicast load.
+#include <cuda.h>
+
+#include "gemm_epilogue.cuh"
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace sd3 {
+
+int encode_tmap_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t inner,
+                   uint64_t outer, uint64_t ld_bytes, uint32_t box_inner, uint32_t box_outer);
+int device_sm_count();
+
+namespace {
+
+using namespace gemm_detail;
+
+constexpr int P_BM = 128;            // rows of A per CTA (256 per pair)
+constexpr int P_BN = 256;            // output columns per pair tile
+constexpr int P_BN_HALF = 128;       // rows of W each CTA loads
+constexpr int P_KBYTES = 128;        // bytes of K per stage row (64 bf16)
+constexpr int P_A_BYTES = P_BM * P_KBYTES;
+constexpr int P_B_BYTES = P_BN_HALF * P_KBYTES;
+constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;  // 32 KiB
+constexpr int P_STAGES = 6;
+constexpr int P_TMEM_COLS = 512;     // two accumulators of 256 columns
+constexpr int P_THREADS = 64 + 32 * EPI_WARPS;
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 256 + 1024;
+
+template <int EPI, bool OUT_F32>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
+gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
+                         const __grid_constant__ CUtensorMap tmW, const GemmArgs g) {
+  constexpr uint32_t IDESC = make_idesc(1, 1, 2 * P_BM, P_BN, 0, 0);  // M = 256 across the pair
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + P_STAGES * P_STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + P_STAGES;
+  uint64_t* tfull_bar = empty_bar + P_STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);   // leader's expect_tx arrival; bytes of both CTAs
+      mbar_init(&empty_bar[s], 1);  // one multicast commit per use
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 2 * EPI_WARPS);  // epilogue warps of both CTAs (leader's copy is used)
+    }
+    *s_abort = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmW);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, P_TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised before any remote signal
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const WaitCtx wc{s_abort, g.status};
+
+  const int num_tiles = g.tiles_m * g.tiles_n;  // tiles of 256 x 256
+  const int KB = g.k_blocks;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      const int m0 = (tile / g.tiles_n) * (2 * P_BM) + static_cast<int>(rank) * P_BM;
+      const int n0 = (tile % g.tiles_n) * P_BN + static_cast<int>(rank) * P_BN_HALF;
+      for (int kb = 0; kb < KB; ++kb) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1, wc, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
+        if (lane == 0) {
+          uint8_t* sa = smem + stage * P_STAGE_BYTES;
+          // all bytes of the stage (both CTAs) are credited to the leader's barrier
+          const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * P_STAGE_BYTES);
+          tma_load_2d_pair(sa, &tmA, bar, kb * 64, m0);
+          tma_load_2d_pair(sa + P_A_BYTES, &tmW, bar, kb * 64, n0);
+        }
+        __syncwarp();
+        if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (leader only) ------------------
+    if (rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, wc, DEV_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * P_BN);
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, wc, DEV_TIMEOUT_FULL)) { ok = false; break; }
+          tc_fence_after_sync();
+          if (lane == 0) {
+            const uint32_t a_addr = smem_u32(smem + stage * P_STAGE_BYTES);
+            const uint64_t a_desc = make_smem_desc_sw128(a_addr, 16, 1024);
+            const uint64_t b_desc = make_smem_desc_sw128(a_addr + P_A_BYTES, 16, 1024);
+#pragma unroll
+            for (int k = 0; k < P_KBYTES / 32; ++k) {
+              const uint64_t adv = static_cast<uint64_t>((k * 32) >> 4);
+              mma_f16_ss_pair(d_tmem, a_desc + adv, b_desc + adv, IDESC, (kb | k) != 0);
+            }
+            mma_commit_pair(&empty_bar[stage], 3);          // frees the stage in both CTAs
+            if (kb == KB - 1) mma_commit_pair(&tfull_bar[acc], 3);  // accumulator ready in both CTAs
+          }
+          __syncwarp();
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        }
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (both CTAs) ----------------------
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int row = quad * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs) {
+      const int m0 = (tile / g.tiles_n) * (2 * P_BM) + static_cast<int>(rank) * P_BM;
+      const int n0 = (tile % g.tiles_n) * P_BN;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
+                             static_cast<uint32_t>(acc * P_BN);
+      if (!drain_tile<P_BN, EPI, OUT_F32>(t_row, m0 + row, n0, half, g, &tfull_bar[acc], acc_phase, wc))
+        break;
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*s_abort) drain_after_abort();
+  cluster_sync_all();  // no remote arrival or multicast commit may target an exited CTA
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, P_TMEM_COLS);
+  }
+}
+
+template <int EPI, bool OUT_F32>
+int launch_pair_inst(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmArgs& g,
+                     cudaStream_t stream) {
+  auto kern = gemm_pair_tcgen05_kernel<EPI, OUT_F32>;
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
+    if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(gemm_pair)");
+    attr_done[dev] = true;
+  }
+  const int tiles = g.tiles_m * g.tiles_n;
+  const int max_pairs = device_sm_count() / 2;
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  kern<<<2 * pairs, P_THREADS, P_SMEM_BYTES, stream>>>(tmA, tmW, g);
+  return after_launch("gemm_pair_tcgen05_kernel");
+}
+
+}  // namespace
+
+// Whether the CTA-pair kernel covers this problem (bf16 operands, N a multiple
+// of 256, enough rows to fill pair tiles).
+bool gemm_pair_supported(int operand_dtype, int M, int N, int K, const GemmEpilogue& epi) {
+  (void)K;
+  if (operand_dtype != OPERAND_BF16) return false;
+  if (N % P_BN != 0 || M < 2 * P_BM) return false;
+  if (epi.mode == EPI_UNPATCHIFY) return false;
+  return true;
+}
+
+int launch_gemm_pair(const void* A, long lda, const void* W, long ldw, int M, int N, int K,
+                     const GemmEpilogue& epi, int* dev_status, cudaStream_t stream) {
+  GemmArgs g;
+  g.M = M; g.N = N; g.K = K;
+  g.k_blocks = (K + 63) / 64;
+  g.tiles_m = (M + 2 * P_BM - 1) / (2 * P_BM);
+  g.tiles_n = N / P_BN;
+  g.epi = epi;
+  g.status = dev_status;
+  CUtensorMap tmA, tmW;
+  int rc = encode_tmap_2d(&tmA, A, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, 64, P_BM);
+  if (rc) return rc;
+  rc = encode_tmap_2d(&tmW, W, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldw * 2, 64, P_BN_HALF);
+  if (rc) return rc;
+  const bool f32 = epi.out_f32 != 0;
+  switch (epi.mode) {
+    case EPI_BIAS:
+      return f32 ? launch_pair_inst<EPI_BIAS, true>(tmA, tmW, g, stream)
+                 : launch_pair_inst<EPI_BIAS, false>(tmA, tmW, g, stream);
+    case EPI_BIAS_GELU:
+      return f32 ? launch_pair_inst<EPI_BIAS_GELU, true>(tmA, tmW, g, stream)
+                 : launch_pair_inst<EPI_BIAS_GELU, false>(tmA, tmW, g, stream);
+    case EPI_GATE_RESID:
+      if (!f32) break;
+      return launch_pair_inst<EPI_GATE_RESID, true>(tmA, tmW, g, stream);
+    case EPI_QKV_NORM:
+      return f32 ? launch_pair_inst<EPI_QKV_NORM, true>(tmA, tmW, g, stream)
+                 : launch_pair_inst<EPI_QKV_NORM, false>(tmA, tmW, g, stream);
+    case EPI_ADD_TABLE:
+      if (!f32) break;
+      return launch_pair_inst<EPI_ADD_TABLE, true>(tmA, tmW, g, stream);
+    default:
+      break;
+  }
+  set_last_error("gemm_pair: unsupported epilogue mode %d / out_f32 %d", epi.mode, epi.out_f32);
+  return ST_UNSUPPORTED;
+}
+
+}  // namespace sd3

@@ -178,7 +178,7 @@ template <> struct WChunk<float> {
 // all weight loads of a slab are issued before any of them is consumed, so a
 // warp keeps R * KU * 512 bytes of weight reads in flight.
 template <typename WT, int R, int BC, int KU>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 skinny_linear_kernel(const float* __restrict__ in, long ld_in, const WT* __restrict__ W,
                      const float* __restrict__ bias, const float* __restrict__ add, long ld_add,
                      float* __restrict__ out, long ld_out, int B, int N, int K, int act_out) {
@@ -381,15 +381,22 @@ int launch_skinny_linear(const float* in, long ld_in, const void* W, int w_f32, 
     set_last_error("skinny_linear: invalid argument (K %d must be a multiple of 8)", K);
     return ST_INVALID_ARG;
   }
-  constexpr int R = 2, BC = 8, WPB = 8;
-  const long warps = (static_cast<long>(N) + R - 1) / R;
-  const unsigned grid = static_cast<unsigned>((warps + WPB - 1) / WPB);
-  if (w_f32)
-    skinny_linear_kernel<float, R, BC, 3><<<grid, WPB * 32, 0, stream>>>(
+  // R output columns per warp: every activation chunk read from L1 is reused R
+  // times, so larger R keeps the L1 traffic per weight byte low.
+  constexpr int BC = 8, WPB = 4;
+  if (w_f32) {
+    constexpr int R = 4;
+    const long warps = (static_cast<long>(N) + R - 1) / R;
+    const unsigned grid = static_cast<unsigned>((warps + WPB - 1) / WPB);
+    skinny_linear_kernel<float, R, BC, 2><<<grid, WPB * 32, 0, stream>>>(
         in, ld_in, static_cast<const float*>(W), bias, add, ld_add, out, ld_out, B, N, K, act_out);
-  else
-    skinny_linear_kernel<bf16, R, BC, 6><<<grid, WPB * 32, 0, stream>>>(
+  } else {
+    constexpr int R = 8;
+    const long warps = (static_cast<long>(N) + R - 1) / R;
+    const unsigned grid = static_cast<unsigned>((warps + WPB - 1) / WPB);
+    skinny_linear_kernel<bf16, R, BC, 2><<<grid, WPB * 32, 0, stream>>>(
         in, ld_in, static_cast<const bf16*>(W), bias, add, ld_add, out, ld_out, B, N, K, act_out);
+  }
   return after_launch("skinny_linear_kernel");
 }
 

@@ -356,3 +356,12 @@ class Model:
         check(lib().sd3_block_forward(self.handle, layer, ptr(y), ptr(c), ptr(x), B, Tc, Tx,
                                       stream_ptr()), "sd3_block_forward")
         return c, x
+
+
+def shard_range(n, world, rank):
+    """Contiguous slice [lo, hi) of n independent samples owned by `rank` of
+    `world` ranks (sizes differ by at most one).  Samples never interact in the
+    denoiser, so batch sharding needs no collective on the data path."""
+    base, rem = divmod(n, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
