@@ -155,38 +155,43 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
 
     // S_u = Q K_u^T for sub-tile u into score buffer (u & 1); releases the K
     // stage after its second half (or after the last sub-tile).
-    auto issue_s = [&](int u) -> bool {
+    auto issue_s = [&](int u, bool k_ready) -> bool {
       const int j = u >> 1, st = j % AT_STAGES;
-      if ((u & 1) == 0) {
+      if ((u & 1) == 0 && !k_ready) {
         if (!mbar_wait(&k_full[st], (j / AT_STAGES) & 1, wc, DEV_TIMEOUT_ATTN_KV)) return false;
-        tc_fence_after_sync();
       }
-      if (lane == 0) {
-        const uint32_t s_tmem = tmem_base + AT_S_COL + (u & 1) * AT_SUB;
-        const uint64_t k_desc = make_smem_desc_sw128(
-            smem_u32(k_smem + st * AT_TILE_BYTES + (u & 1) * AT_SUB_BYTES), 16, 1024);
+      tc_fence_after_sync();
+      const uint32_t s_tmem = tmem_base + AT_S_COL + (u & 1) * AT_SUB;
+      const uint64_t k_desc = make_smem_desc_sw128(
+          smem_u32(k_smem + st * AT_TILE_BYTES + (u & 1) * AT_SUB_BYTES), 16, 1024);
 #pragma unroll
-        for (int k = 0; k < AT_D / 16; ++k)
-          mma_f16_ss(s_tmem, q_desc + 2 * k, k_desc + 2 * k, IDESC_S, k != 0);
-        mma_commit(&s_full[u & 1]);
-        if ((u & 1) == 1 || u == nsub - 1) mma_commit(&k_empty[st]);
-      }
-      __syncwarp();
+      for (int k = 0; k < AT_D / 16; ++k)
+        mma_f16_ss(s_tmem, q_desc + 2 * k, k_desc + 2 * k, IDESC_S, k != 0);
+      mma_commit(&s_full[u & 1]);
+      if ((u & 1) == 1 || u == nsub - 1) mma_commit(&k_empty[st]);
       return true;
     };
 
-    bool ok = mbar_wait(q_full, 0, wc, DEV_TIMEOUT_ATTN_Q);
-    if (ok) ok = issue_s(0);
-    if (ok && nsub > 1) ok = issue_s(1);
-    for (int t = 0; t < nsub && ok; ++t) {
-      const int j = t >> 1, st = j % AT_STAGES;
-      // O += P_t V_t
-      if (!mbar_wait(&p_ready[t & 1], (t >> 1) & 1, wc, DEV_TIMEOUT_ATTN_P)) break;
-      if ((t & 1) == 0) {
-        if (!mbar_wait(&v_full[st], (j / AT_STAGES) & 1, wc, DEV_TIMEOUT_ATTN_KV)) break;
-      }
-      tc_fence_after_sync();
-      if (lane == 0) {
+    if (lane == 0) {  // a single thread runs the whole issue loop
+      bool ok = mbar_wait(q_full, 0, wc, DEV_TIMEOUT_ATTN_Q);
+      if (ok) ok = issue_s(0, false);
+      if (ok && nsub > 1) ok = issue_s(1, false);
+      for (int t = 0; t < nsub && ok; ++t) {
+        const int j = t >> 1, st = j % AT_STAGES;
+        // While P_t is still being produced, test the barriers the next issues
+        // will need, so their latency is off the critical path.
+        uint32_t v_ready = 1, k_ready = 1;
+        if ((t & 1) == 0) v_ready = mbar_test_wait(&v_full[st], (j / AT_STAGES) & 1);
+        if (t + 2 < nsub && (t & 1) == 0) {
+          const int j2 = (t + 2) >> 1;
+          k_ready = mbar_test_wait(&k_full[j2 % AT_STAGES], (j2 / AT_STAGES) & 1);
+        }
+        // O += P_t V_t
+        if (!mbar_wait(&p_ready[t & 1], (t >> 1) & 1, wc, DEV_TIMEOUT_ATTN_P)) break;
+        if (!v_ready) {
+          if (!mbar_wait(&v_full[st], (j / AT_STAGES) & 1, wc, DEV_TIMEOUT_ATTN_KV)) break;
+        }
+        tc_fence_after_sync();
         const uint32_t p_tmem = tmem_base + AT_S_COL + (t & 1) * AT_SUB;
         const uint64_t v_desc = make_smem_desc_sw128(
             smem_u32(v_smem + st * AT_TILE_BYTES + (t & 1) * AT_SUB_BYTES), 1024, 1024);
@@ -199,11 +204,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
         mma_commit(pv_done);
         if ((t & 1) == 1 || t == nsub - 1) mma_commit(&v_empty[st]);
         if (t == nsub - 1) mma_commit(o_full);
+        // the buffer of P_t is free once that product has been issued (the
+        // tensor pipe executes in issue order): refill it with S_{t+2}
+        if (t + 2 < nsub) ok = issue_s(t + 2, k_ready != 0);
       }
-      __syncwarp();
-      // the buffer of P_t is free once that product has been issued (the
-      // tensor pipe executes in issue order): refill it with S_{t+2}
-      if (t + 2 < nsub) ok = issue_s(t + 2);
     }
   } else {
     // ------------------------------ softmax + epilogue ------------------------
@@ -215,13 +219,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
     float m_used = -INFINITY;  // running max (raw score units) the exponentials refer to
     float l = 0.f;
     bool ok = true;
+    bool fetched = false;  // scores of sub-tile t already requested from TMEM
+    uint32_t r0[32], r1[32];
     for (int t = 0; t < nsub; ++t) {
       const uint32_t s_tmem = lane_base + AT_S_COL + (t & 1) * AT_SUB;
-      if (!mbar_wait(&s_full[t & 1], (t >> 1) & 1, wc, DEV_TIMEOUT_ATTN_S)) { ok = false; break; }
-      tc_fence_after_sync();
-      uint32_t r0[32], r1[32];
-      tmem_ld_32x32b_x32(s_tmem, r0);
-      tmem_ld_32x32b_x32(s_tmem + 32, r1);
+      if (!fetched) {
+        if (!mbar_wait_warp(&s_full[t & 1], (t >> 1) & 1, wc, DEV_TIMEOUT_ATTN_S)) { ok = false; break; }
+        tc_fence_after_sync();
+        tmem_ld_32x32b_x32(s_tmem, r0);
+        tmem_ld_32x32b_x32(s_tmem + 32, r1);
+      }
       tmem_wait_ld();
       const int kv0 = t * AT_SUB;
       if (kv0 + AT_SUB > T) {  // ragged last sub-tile: keys >= T do not exist
@@ -253,7 +260,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
           }
           // P_{t-1} V_{t-1} must have landed in O before O is rescaled; the
           // product of this sub-tile is only issued after p_ready below.
-          if (!mbar_wait(pv_done, (t - 1) & 1, wc, DEV_TIMEOUT_ATTN_O)) { ok = false; break; }
+          if (!mbar_wait_warp(pv_done, (t - 1) & 1, wc, DEV_TIMEOUT_ATTN_O)) { ok = false; break; }
           tc_fence_after_sync();
           uint32_t o0[32];
           tmem_ld_32x32b_x32(o_tmem, o0);
@@ -285,12 +292,27 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
       }
       tmem_st_32x32b_x32(s_tmem, pk);
       l += ls0 + ls1;
+      // If the next scores are already there (they normally are: S is issued one
+      // sub-tile ahead), request them now so the TMEM load overlaps the hand-off.
+      fetched = false;
+      if (t + 1 < nsub) {
+        uint32_t rdy = 0;
+        if (lane == 0) rdy = mbar_test_wait(&s_full[(t + 1) & 1], ((t + 1) >> 1) & 1);
+        rdy = __shfl_sync(0xffffffffu, rdy, 0);
+        if (rdy) {
+          tc_fence_after_sync();
+          const uint32_t s_next = lane_base + AT_S_COL + ((t + 1) & 1) * AT_SUB;
+          tmem_ld_32x32b_x32(s_next, r0);
+          tmem_ld_32x32b_x32(s_next + 32, r1);
+          fetched = true;
+        }
+      }
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[t & 1]);
     }
-    if (ok && mbar_wait(o_full, 0, wc, DEV_TIMEOUT_ATTN_O)) {
+    if (ok && mbar_wait_warp(o_full, 0, wc, DEV_TIMEOUT_ATTN_O)) {
       tc_fence_after_sync();
       uint32_t o0[32], o1[32];
       tmem_ld_32x32b_x32(o_tmem, o0);

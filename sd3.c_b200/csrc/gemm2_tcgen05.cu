@@ -17,6 +17,10 @@
 // Loads are plain tiled TMA (cta_group::2 form so the peer's transaction bytes
 // can be credited to the leader's barrier); nothing here is a multicast load.
 #include <cuda.h>
+#include <stdio.h>
+#include <stdlib.h>
+
+#include <vector>
 
 #include "gemm_epilogue.cuh"
 #include "kernels.h"
@@ -39,7 +43,7 @@ constexpr int P_KBYTES = 128;        // bytes of K per stage row (64 bf16)
 constexpr int P_A_BYTES = P_BM * P_KBYTES;
 constexpr int P_B_BYTES = P_BN_HALF * P_KBYTES;
 constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;  // 32 KiB
-constexpr int P_STAGES = 6;
+constexpr int P_STAGES = 7;
 constexpr int P_TMEM_COLS = 512;     // two accumulators of 256 columns
 constexpr int P_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 256 + 1024;
@@ -47,7 +51,8 @@ constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 256 + 1024;
 template <int EPI, bool OUT_F32>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
-                         const __grid_constant__ CUtensorMap tmW, const GemmArgs g) {
+                         const __grid_constant__ CUtensorMap tmW, const GemmArgs g,
+                         long long* __restrict__ probe, int skip_loads) {
   constexpr uint32_t IDESC = make_idesc(1, 1, 2 * P_BM, P_BN, 0, 0);  // M = 256 across the pair
 
   extern __shared__ uint8_t smem_raw[];
@@ -94,29 +99,36 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   const int num_tiles = g.tiles_m * g.tiles_n;  // tiles of 256 x 256
   const int KB = g.k_blocks;
 
-  if (warp == 0) {
-    // ------------------------------ TMA producer (both CTAs) ------------------
+  if (warp == 0 && lane == 0) {
+    // ------------------------------ TMA producer (both CTAs, one thread) ------
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    long long w_empty = 0;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
       const int m0 = (tile / g.tiles_n) * (2 * P_BM) + static_cast<int>(rank) * P_BM;
       const int n0 = (tile % g.tiles_n) * P_BN + static_cast<int>(rank) * P_BN_HALF;
       for (int kb = 0; kb < KB; ++kb) {
+        const long long c0 = probe ? clock64() : 0;
         if (!mbar_wait(&empty_bar[stage], phase ^ 1, wc, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
-        if (lane == 0) {
+        if (probe) w_empty += clock64() - c0;
+        {
           uint8_t* sa = smem + stage * P_STAGE_BYTES;
           // all bytes of the stage (both CTAs) are credited to the leader's barrier
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
-          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * P_STAGE_BYTES);
-          tma_load_2d_pair(sa, &tmA, bar, kb * 64, m0);
-          tma_load_2d_pair(sa + P_A_BYTES, &tmW, bar, kb * 64, n0);
+          if (skip_loads && (tile != pair || kb >= P_STAGES)) {
+            if (rank == 0) mbar_arrive(&full_bar[stage]);  // experiment: reuse stale operands
+          } else {
+            if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * P_STAGE_BYTES);
+            tma_load_2d_pair(sa, &tmA, bar, kb * 64, m0);
+            tma_load_2d_pair(sa + P_A_BYTES, &tmW, bar, kb * 64, n0);
+          }
         }
-        __syncwarp();
         if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
       }
     }
-  } else if (warp == 1) {
+    if (probe) probe[blockIdx.x * 8 + 0] = w_empty;
+  } else if (warp == 1 && lane == 0) {
     // ------------------------------ MMA issuer (leader only) ------------------
     if (rank == 0) {
       int stage = 0;
@@ -124,14 +136,30 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      long long w_full = 0, w_tempty = 0;
+      bool stage_ready = false;
+      const long long t_begin = probe ? clock64() : 0;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const long long c0 = probe ? clock64() : 0;
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, wc, DEV_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        if (probe) w_tempty += clock64() - c0;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * P_BN);
         for (int kb = 0; kb < KB; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, wc, DEV_TIMEOUT_FULL)) { ok = false; break; }
+          // The readiness of this stage was tested while the previous stage's
+          // MMAs were being issued; only fall back to a blocking wait if that
+          // early test failed.
+          if (!stage_ready) {
+            const long long c1 = probe ? clock64() : 0;
+            if (!mbar_wait(&full_bar[stage], phase, wc, DEV_TIMEOUT_FULL)) { ok = false; break; }
+            if (probe) w_full += clock64() - c1;
+          }
+          int ns = stage + 1;
+          uint32_t np = phase;
+          if (ns == P_STAGES) { ns = 0; np ^= 1; }
+          const uint32_t next_ready = mbar_test_wait(&full_bar[ns], np);  // result consumed after the MMAs
           tc_fence_after_sync();
-          if (lane == 0) {
+          {
             const uint32_t a_addr = smem_u32(smem + stage * P_STAGE_BYTES);
             const uint64_t a_desc = make_smem_desc_sw128(a_addr, 16, 1024);
             const uint64_t b_desc = make_smem_desc_sw128(a_addr + P_A_BYTES, 16, 1024);
@@ -143,32 +171,48 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             mma_commit_pair(&empty_bar[stage], 3);          // frees the stage in both CTAs
             if (kb == KB - 1) mma_commit_pair(&tfull_bar[acc], 3);  // accumulator ready in both CTAs
           }
-          __syncwarp();
-          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+          stage = ns;
+          phase = np;
+          stage_ready = next_ready != 0;
         }
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
+      if (probe) {
+        probe[blockIdx.x * 8 + 1] = w_full;
+        probe[blockIdx.x * 8 + 2] = w_tempty;
+        probe[blockIdx.x * 8 + 3] = clock64() - t_begin;
+      }
     }
-  } else {
+  } else if (warp >= 2) {
     // ------------------------------ epilogue (both CTAs) ----------------------
     const int quad = warp & 3;
     const int half = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
+    long long t_epi = 0, w_epi[3] = {0, 0, 0};
     for (int tile = pair; tile < num_tiles; tile += num_pairs) {
       const int m0 = (tile / g.tiles_n) * (2 * P_BM) + static_cast<int>(rank) * P_BM;
       const int n0 = (tile % g.tiles_n) * P_BN;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                              static_cast<uint32_t>(acc * P_BN);
-      if (!drain_tile<P_BN, EPI, OUT_F32>(t_row, m0 + row, n0, half, g, &tfull_bar[acc], acc_phase, wc))
+      const long long c0 = probe ? clock64() : 0;
+      if (!drain_tile<P_BN, EPI, OUT_F32>(t_row, m0 + row, n0, half, g, &tfull_bar[acc], acc_phase, wc,
+                                          probe ? w_epi : nullptr))
         break;
+      if (probe) t_epi += clock64() - c0;  // includes the wait for the accumulator
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
+    }
+    if (probe && warp == 2 && lane == 0) {
+      probe[blockIdx.x * 8 + 4] = t_epi;
+      probe[blockIdx.x * 8 + 5] = w_epi[0];
+      probe[blockIdx.x * 8 + 6] = w_epi[1];
+      probe[blockIdx.x * 8 + 7] = w_epi[2];
     }
   }
 
@@ -198,8 +242,38 @@ int launch_pair_inst(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmA
   const int tiles = g.tiles_m * g.tiles_n;
   const int max_pairs = device_sm_count() / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
-  kern<<<2 * pairs, P_THREADS, P_SMEM_BYTES, stream>>>(tmA, tmW, g);
-  return after_launch("gemm_pair_tcgen05_kernel");
+  // Diagnostic: SD3_GEMM_PROBE=1 makes every launch synchronous and prints where
+  // the roles of the kernel spent their cycles (averages over CTAs).
+  static const bool probing = []() {
+    const char* v = getenv("SD3_GEMM_PROBE");
+    return v && (v[0] == '1' || v[0] == '2');
+  }();
+  static const int skip_loads = []() {
+    const char* v = getenv("SD3_GEMM_PROBE");
+    return (v && v[0] == '2') ? 1 : 0;
+  }();
+  long long* probe = nullptr;
+  if (probing && g.status) {  // never on the allocation-free entry point (no status word there)
+    if (cudaMalloc(&probe, sizeof(long long) * 8 * 2 * pairs) != cudaSuccess) probe = nullptr;
+    if (probe) cudaMemset(probe, 0, sizeof(long long) * 8 * 2 * pairs);
+  }
+  kern<<<2 * pairs, P_THREADS, P_SMEM_BYTES, stream>>>(tmA, tmW, g, probe, skip_loads);
+  const int rc = after_launch("gemm_pair_tcgen05_kernel");
+  if (probe) {
+    std::vector<long long> h(8 * 2 * pairs);
+    cudaStreamSynchronize(stream);
+    cudaMemcpy(h.data(), probe, h.size() * sizeof(long long), cudaMemcpyDeviceToHost);
+    cudaFree(probe);
+    double s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int c = 0; c < 2 * pairs; ++c)
+      for (int i = 0; i < 8; ++i) s[i] += static_cast<double>(h[c * 8 + i]);
+    fprintf(stderr,
+            "[gemm_pair probe] M %d N %d K %d epi %d: mma loop %.0f clk/CTA (wait operands %.0f, wait "
+            "epilogue %.0f), producer wait-empty %.0f, epilogue warp total %.0f: waiting %.0f, TMEM loads %.0f, math+stores %.0f\n",
+            g.M, g.N, g.K, g.epi.mode, s[3] / pairs, s[1] / pairs, s[2] / pairs, s[0] / (2 * pairs),
+            s[4] / (2 * pairs), s[5] / (2 * pairs), s[6] / (2 * pairs), s[7] / (2 * pairs));
+  }
+  return rc;
 }
 
 }  // namespace
@@ -223,6 +297,11 @@ int launch_gemm_pair(const void* A, long lda, const void* W, long ldw, int M, in
   g.tiles_n = N / P_BN;
   g.epi = epi;
   g.status = dev_status;
+  {
+    const long esz = epi.out_f32 ? 4 : 2;
+    g.wide_store = (N % 16 == 0) && ((epi.ldo * esz) % 32 == 0) &&
+                   ((reinterpret_cast<uintptr_t>(epi.out) & 31) == 0);
+  }
   CUtensorMap tmA, tmW;
   int rc = encode_tmap_2d(&tmA, A, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, 64, P_BM);
   if (rc) return rc;

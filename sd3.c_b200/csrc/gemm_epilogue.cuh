@@ -2,6 +2,12 @@
 // variants): bias / GELU-tanh / gate+residual / per-head QK-RMSNorm with token
 // re-mapping / position-table add / unpatchify, applied to accumulator rows read
 // from TMEM (one output row per thread).
+//
+// Two things keep these epilogues off the critical path: every per-column
+// parameter a chunk needs (bias, gate, residual) is requested in one batch
+// BEFORE the accumulator load is waited for, so one memory latency is exposed
+// per chunk instead of one per 8 columns; and rows are written with 32-byte
+// stores (a full sector per thread) whenever the output is 32-byte aligned.
 #pragma once
 #include "kernels.h"
 #include "ptx.cuh"
@@ -16,6 +22,7 @@ struct GemmArgs {
   int k_blocks;      // ceil(K / elements per stage)
   int tiles_m, tiles_n;
   GemmEpilogue epi;
+  int wide_store;    // output rows are 32-byte aligned at every 16-column (bf16) / 8-column (f32) group
   int* status;
 };
 
@@ -27,8 +34,49 @@ __device__ __forceinline__ float gelu_tanh_f(float x) {
   return 0.5f * x * (1.0f + t);
 }
 
+__device__ __forceinline__ void st_global_32B(void* p, uint32_t a0, uint32_t a1, uint32_t a2,
+                                              uint32_t a3, uint32_t a4, uint32_t a5, uint32_t a6,
+                                              uint32_t a7) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a0),
+               "r"(a1), "r"(a2), "r"(a3), "r"(a4), "r"(a5), "r"(a6), "r"(a7)
+               : "memory");
+}
+
+// 16 consecutive output values of one row
 template <bool OUT_F32>
-__device__ __forceinline__ void store8(void* out, long idx, const float (&o)[8]) {
+__device__ __forceinline__ void store16(void* out, long idx, const float* o, bool wide) {
+  if constexpr (OUT_F32) {
+    float* p = static_cast<float*>(out) + idx;
+    if (wide) {
+      st_global_32B(p, __float_as_uint(o[0]), __float_as_uint(o[1]), __float_as_uint(o[2]),
+                    __float_as_uint(o[3]), __float_as_uint(o[4]), __float_as_uint(o[5]),
+                    __float_as_uint(o[6]), __float_as_uint(o[7]));
+      st_global_32B(p + 8, __float_as_uint(o[8]), __float_as_uint(o[9]), __float_as_uint(o[10]),
+                    __float_as_uint(o[11]), __float_as_uint(o[12]), __float_as_uint(o[13]),
+                    __float_as_uint(o[14]), __float_as_uint(o[15]));
+    } else {
+      float4* q = reinterpret_cast<float4*>(p);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) q[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+    }
+  } else {
+    bf16* p = static_cast<bf16*>(out) + idx;
+    uint32_t u[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) u[i] = pack_bf16x2(o[2 * i], o[2 * i + 1]);
+    if (wide) {
+      st_global_32B(p, u[0], u[1], u[2], u[3], u[4], u[5], u[6], u[7]);
+    } else {
+      uint4* q = reinterpret_cast<uint4*>(p);
+      q[0] = make_uint4(u[0], u[1], u[2], u[3]);
+      q[1] = make_uint4(u[4], u[5], u[6], u[7]);
+    }
+  }
+}
+
+// 8 consecutive output values (16-byte stores); used for ragged N
+template <bool OUT_F32>
+__device__ __forceinline__ void store8(void* out, long idx, const float* o) {
   if constexpr (OUT_F32) {
     float4* p = reinterpret_cast<float4*>(static_cast<float*>(out) + idx);
     p[0] = make_float4(o[0], o[1], o[2], o[3]);
@@ -43,68 +91,81 @@ __device__ __forceinline__ void store8(void* out, long idx, const float (&o)[8])
   }
 }
 
-__device__ __forceinline__ void load8(const float* p, float (&o)[8]) {
-  const float4 a = __ldg(reinterpret_cast<const float4*>(p));
-  const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
-  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w;
-  o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+// `count` groups of 4 floats starting at p into dst (zeros past column N)
+template <int GROUPS>
+__device__ __forceinline__ void load_f4_batch(const float* p, int n_base, int N, float (&dst)[GROUPS * 4]) {
+#pragma unroll
+  for (int i = 0; i < GROUPS; ++i) {
+    float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (p != nullptr && n_base + i * 4 < N) t = __ldg(reinterpret_cast<const float4*>(p + n_base) + i);
+    dst[4 * i] = t.x; dst[4 * i + 1] = t.y; dst[4 * i + 2] = t.z; dst[4 * i + 3] = t.w;
+  }
 }
 
-// Epilogue for 64 consecutive accumulator columns of one row.
+// same, through ordinary (coherent) loads: for data this kernel also writes
+template <int GROUPS>
+__device__ __forceinline__ void load_f4_batch_rw(const float* p, int n_base, int N, float (&dst)[GROUPS * 4]) {
+#pragma unroll
+  for (int i = 0; i < GROUPS; ++i) {
+    float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (n_base + i * 4 < N) t = *(reinterpret_cast<const float4*>(p + n_base) + i);
+    dst[4 * i] = t.x; dst[4 * i + 1] = t.y; dst[4 * i + 2] = t.z; dst[4 * i + 3] = t.w;
+  }
+}
+
+struct RowMap {
+  int b;      // sample index of the row
+  int t_in;   // row within the sample (GEMM side)
+  long orow;  // output row
+};
+
+__device__ __forceinline__ RowMap map_row(int m, const GemmEpilogue& e) {
+  RowMap r;
+  r.b = 0;
+  r.t_in = m;
+  r.orow = m;
+  if (e.rows_in > 0) {
+    r.b = m / e.rows_in;
+    r.t_in = m - r.b * e.rows_in;
+    r.orow = static_cast<long>(r.b) * e.rows_out + e.row_off + r.t_in;
+  }
+  return r;
+}
+
+// Epilogue for 64 consecutive accumulator columns of one row; v already holds
+// acc * alpha + bias.
 template <int EPI, bool OUT_F32>
-__device__ __forceinline__ void epilogue_64(float (&v)[64], int m, int n_base,
+__device__ __forceinline__ void epilogue_64(float (&v)[64], const RowMap& rm, int n_base,
                                             const GemmArgs& g) {
   const GemmEpilogue& e = g.epi;
   const int N = g.N;
-  int b = 0;
-  long orow = m;
-  int t_in = m;
-  if (e.rows_in > 0) {
-    b = m / e.rows_in;
-    t_in = m - b * e.rows_in;
-    orow = static_cast<long>(b) * e.rows_out + e.row_off + t_in;
-  }
-  // bias (and dequantisation scale)
-#pragma unroll
-  for (int gi = 0; gi < 8; ++gi) {
-    const int n = n_base + gi * 8;
-    if (n < N) {
-      float bb[8];
-      if (e.bias) {
-        load8(e.bias + n, bb);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) bb[j] = 0.f;
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[gi * 8 + j] = fmaf(v[gi * 8 + j], e.alpha, bb[j]);
-    }
-  }
   if constexpr (EPI == EPI_QKV_NORM) {
     if (e.do_norm && n_base < e.qk_cols) {
-      float ss = 0.f;
-#pragma unroll
-      for (int j = 0; j < 64; ++j) ss = fmaf(v[j], v[j], ss);
-      const float r = rsqrtf(ss * (1.0f / 64.0f) + e.eps);
       const float* w = (n_base < (e.qk_cols >> 1)) ? e.wq : e.wk;
+      float ww[64];
+      if (w) {
+        load_f4_batch<16>(w, 0, 64, ww);  // in flight while the statistic is formed
+      } else {
 #pragma unroll
-      for (int gi = 0; gi < 8; ++gi) {
-        float ww[8];
-        if (w) {
-          load8(w + gi * 8, ww);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) ww[j] = 1.f;
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[gi * 8 + j] = v[gi * 8 + j] * r * ww[j];
+        for (int j = 0; j < 64; ++j) ww[j] = 1.f;
       }
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 64; j += 4) {
+        s0 = fmaf(v[j], v[j], s0);
+        s1 = fmaf(v[j + 1], v[j + 1], s1);
+        s2 = fmaf(v[j + 2], v[j + 2], s2);
+        s3 = fmaf(v[j + 3], v[j + 3], s3);
+      }
+      const float r = rsqrtf(((s0 + s1) + (s2 + s3)) * (1.0f / 64.0f) + e.eps);
+#pragma unroll
+      for (int j = 0; j < 64; ++j) v[j] = v[j] * r * ww[j];
     }
   }
   if constexpr (EPI == EPI_UNPATCHIFY) {
     // m = (b, r, s) over the patch grid; n = ph * (p * C) + pw * C + c
     const int p = e.up_patch, C = e.up_cin;
-    const int s = t_in % e.up_w, r = t_in / e.up_w;
+    const int s = rm.t_in % e.up_w, r = rm.t_in / e.up_w;
     const long Wpix = static_cast<long>(e.up_w) * p, Hpix = static_cast<long>(e.up_h) * p;
     for (int j = 0; j < 64; ++j) {
       const int n = n_base + j;
@@ -112,7 +173,7 @@ __device__ __forceinline__ void epilogue_64(float (&v)[64], int m, int n_base,
       const int c = n % C;
       const int pw = (n / C) % p;
       const int ph = n / (C * p);
-      const long idx = ((static_cast<long>(b) * C + c) * Hpix + (r * p + ph)) * Wpix + (s * p + pw);
+      const long idx = ((static_cast<long>(rm.b) * C + c) * Hpix + (r * p + ph)) * Wpix + (s * p + pw);
       if constexpr (OUT_F32)
         static_cast<float*>(e.out)[idx] = v[j];
       else
@@ -120,132 +181,123 @@ __device__ __forceinline__ void epilogue_64(float (&v)[64], int m, int n_base,
     }
     return;
   }
+  if constexpr (EPI == EPI_BIAS_GELU) {
 #pragma unroll
-  for (int gi = 0; gi < 8; ++gi) {
-    const int n = n_base + gi * 8;
-    if (n >= N) break;
-    float o[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = v[gi * 8 + j];
-    if constexpr (EPI == EPI_BIAS_GELU) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = gelu_tanh_f(o[j]);
-    } else if constexpr (EPI == EPI_GATE_RESID) {
-      float gg[8], rr[8];
-      load8(e.gate + static_cast<long>(b) * e.gate_stride + n, gg);
-      const float4* rp = reinterpret_cast<const float4*>(e.resid + orow * e.ldo + n);
-      const float4 r0 = rp[0], r1 = rp[1];
-      rr[0] = r0.x; rr[1] = r0.y; rr[2] = r0.z; rr[3] = r0.w;
-      rr[4] = r1.x; rr[5] = r1.y; rr[6] = r1.z; rr[7] = r1.w;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = fmaf(gg[j], o[j], rr[j]);
-    } else if constexpr (EPI == EPI_ADD_TABLE) {
-      float tt[8];
-      load8(e.table + static_cast<long>(t_in) * N + n, tt);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] += tt[j];
-    }
-    store8<OUT_F32>(e.out, orow * e.ldo + n, o);
+    for (int j = 0; j < 64; ++j) v[j] = gelu_tanh_f(v[j]);
   }
-}
-
-// Residual row segment of 32 columns into registers (issued early so that the
-// DRAM/L2 latency overlaps the main loop or the previous sub-chunk).
-__device__ __forceinline__ void load_resid32(const float* p, int n_base, int N, float4 (&rr)[8]) {
+  if constexpr (EPI == EPI_ADD_TABLE) {
+    float tt[64];
+    load_f4_batch<16>(e.table + static_cast<long>(rm.t_in) * N, n_base, N, tt);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    if (n_base + i * 4 < N) {
-      asm volatile("ld.global.v4.f32 {%0, %1, %2, %3}, [%4];"
-                   : "=f"(rr[i].x), "=f"(rr[i].y), "=f"(rr[i].z), "=f"(rr[i].w)
-                   : "l"(p + i * 4));
+    for (int j = 0; j < 64; ++j) v[j] += tt[j];
+  }
+  const long base = rm.orow * e.ldo;
+  if (n_base + 64 <= N) {
+#pragma unroll
+    for (int gi = 0; gi < 4; ++gi)
+      store16<OUT_F32>(e.out, base + n_base + gi * 16, &v[gi * 16], g.wide_store != 0);
+  } else {
+#pragma unroll
+    for (int gi = 0; gi < 8; ++gi) {
+      const int n = n_base + gi * 8;
+      if (n < N) store8<OUT_F32>(e.out, base + n, &v[gi * 8]);
     }
   }
 }
-
-// out = resid + gate[b] * (acc * alpha + bias) on 32 columns of one row
-__device__ __forceinline__ void epilogue_gate32(const uint32_t (&acc)[32], const float4 (&rr)[8],
-                                                float* out_row, const float* gate_row, int n_base,
-                                                const GemmArgs& g) {
-  const GemmEpilogue& e = g.epi;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int n = n_base + i * 4;
-    if (n < g.N) {
-      const float4 gg = __ldg(reinterpret_cast<const float4*>(gate_row + n));
-      float4 bb = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (e.bias) bb = __ldg(reinterpret_cast<const float4*>(e.bias + n));
-      float4 o;
-      o.x = fmaf(gg.x, fmaf(__uint_as_float(acc[4 * i + 0]), e.alpha, bb.x), rr[i].x);
-      o.y = fmaf(gg.y, fmaf(__uint_as_float(acc[4 * i + 1]), e.alpha, bb.y), rr[i].y);
-      o.z = fmaf(gg.z, fmaf(__uint_as_float(acc[4 * i + 2]), e.alpha, bb.z), rr[i].z);
-      o.w = fmaf(gg.w, fmaf(__uint_as_float(acc[4 * i + 3]), e.alpha, bb.w), rr[i].w);
-      *reinterpret_cast<float4*>(out_row + n) = o;
-    }
-  }
-}
-
 
 // Drains this warp's share of one accumulator tile (rows = TMEM lanes of the
 // warp's quadrant, columns [half * BN/2, (half+1) * BN/2)) through the epilogue.
 // t_row: TMEM address of the accumulator (lane quadrant and column base applied);
 // m: global output row of this thread; n0: first output column of the tile.
 // Waits for the accumulator on tfull_bar; returns false if that wait gave up.
+// wait_clk (optional, diagnostics): [0] cycles waiting for the accumulator,
+// [1] TMEM loads, [2] math and stores.
 template <int BN, int EPI, bool OUT_F32>
 __device__ __forceinline__ bool drain_tile(uint32_t t_row, int m, int n0, int half, const GemmArgs& g,
-                                           uint64_t* tfull_bar, uint32_t phase, const WaitCtx& wc) {
+                                           uint64_t* tfull_bar, uint32_t phase, const WaitCtx& wc,
+                                           long long* wait_clk = nullptr) {
   constexpr int COLS_PER_WARP = BN / 2;
+  const GemmEpilogue& e = g.epi;
+  const bool valid = m < g.M;
+  const RowMap rm = map_row(valid ? m : 0, e);
   if constexpr (EPI == EPI_GATE_RESID) {
-    // 32 columns at a time; the residual of sub-chunk i+1 is requested before
-    // sub-chunk i is processed, the first one before the accumulator is even
-    // complete.
+    // 32 columns at a time.  Residual, gate and bias of sub-chunk i+1 are
+    // requested before sub-chunk i is processed; those of the first one before
+    // the accumulator is even complete.
     constexpr int NSUB = COLS_PER_WARP / 32;
-    const GemmEpilogue& e = g.epi;
-    const bool valid = m < g.M;
-    const int mm = valid ? m : 0;
-    const int b = mm / e.rows_in;
-    float* out_row = static_cast<float*>(e.out) + static_cast<long>(mm) * e.ldo;
-    const float* res_row = e.resid + static_cast<long>(mm) * e.ldo;
-    const float* gate_row = e.gate + static_cast<long>(b) * e.gate_stride;
+    float* out_row = static_cast<float*>(e.out) + rm.orow * e.ldo;
+    const float* res_row = e.resid + rm.orow * e.ldo;
+    const float* gate_row = e.gate + static_cast<long>(rm.b) * e.gate_stride;
     const int nw = n0 + half * COLS_PER_WARP;
-    float4 rr[8], rn[8];
-    if (valid) load_resid32(res_row + nw, nw, g.N, rr);
-    if (!mbar_wait(tfull_bar, phase, wc, DEV_TIMEOUT_TMEM_FULL)) return false;
+    float rr[32], gg[32], bb[32];
+    if (valid) {
+      load_f4_batch_rw<8>(res_row, nw, g.N, rr);
+      load_f4_batch<8>(gate_row, nw, g.N, gg);
+      load_f4_batch<8>(e.bias, nw, g.N, bb);
+    }
+    const long long c0 = wait_clk ? clock64() : 0;
+    if (!mbar_wait_warp(tfull_bar, phase, wc, DEV_TIMEOUT_TMEM_FULL)) return false;
+    if (wait_clk) wait_clk[0] += clock64() - c0;
     tc_fence_after_sync();
 #pragma unroll
     for (int sub = 0; sub < NSUB; ++sub) {
       const int n_base = nw + sub * 32;
-      if (sub + 1 < NSUB && valid) load_resid32(res_row + n_base + 32, n_base + 32, g.N, rn);
       uint32_t r[32];
       tmem_ld_32x32b_x32(t_row + half * COLS_PER_WARP + sub * 32, r);
       tmem_wait_ld();
-      if (valid && n_base < g.N) epilogue_gate32(r, rr, out_row, gate_row, n_base, g);
-      if (sub + 1 < NSUB) {
+      float o[32];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) rr[i] = rn[i];
+      for (int j = 0; j < 32; ++j)
+        o[j] = fmaf(gg[j], fmaf(__uint_as_float(r[j]), e.alpha, bb[j]), rr[j]);
+      if (sub + 1 < NSUB && valid) {  // next sub-chunk's parameters, in flight during the stores
+        load_f4_batch_rw<8>(res_row, n_base + 32, g.N, rr);
+        load_f4_batch<8>(gate_row, n_base + 32, g.N, gg);
+        load_f4_batch<8>(e.bias, n_base + 32, g.N, bb);
+      }
+      if (valid && n_base < g.N) {
+        if (n_base + 32 <= g.N) {
+          store16<true>(out_row, n_base, &o[0], g.wide_store != 0);
+          store16<true>(out_row, n_base + 16, &o[16], g.wide_store != 0);
+        } else {
+#pragma unroll
+          for (int gi = 0; gi < 4; ++gi)
+            if (n_base + gi * 8 < g.N) store8<true>(out_row, n_base + gi * 8, &o[gi * 8]);
+        }
       }
     }
   } else {
-    if (!mbar_wait(tfull_bar, phase, wc, DEV_TIMEOUT_TMEM_FULL)) return false;
-    tc_fence_after_sync();
     constexpr int CHUNKS = COLS_PER_WARP >= 64 ? COLS_PER_WARP / 64 : 1;
     const bool active = COLS_PER_WARP >= 64 || half == 0;  // BN = 64: one chunk, first half only
     const int c_first = COLS_PER_WARP >= 64 ? half * CHUNKS : 0;
+    float bb[64];
+    if (active) load_f4_batch<16>(e.bias, n0 + c_first * 64, g.N, bb);
+    const long long c0 = wait_clk ? clock64() : 0;
+    if (!mbar_wait_warp(tfull_bar, phase, wc, DEV_TIMEOUT_TMEM_FULL)) return false;
+    if (wait_clk) wait_clk[0] += clock64() - c0;
+    tc_fence_after_sync();
 #pragma unroll 1
     for (int ci = 0; ci < CHUNKS; ++ci) {
       const int c = c_first + ci;
       const int n_base = n0 + c * 64;
       if (!active || n_base >= g.N) break;  // warp-uniform
       uint32_t r0[32], r1[32];
+      const long long c1 = wait_clk ? clock64() : 0;
       tmem_ld_32x32b_x32(t_row + c * 64, r0);
       tmem_ld_32x32b_x32(t_row + c * 64 + 32, r1);
       tmem_wait_ld();
+      const long long c2 = wait_clk ? clock64() : 0;
       float v[64];
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
-        v[j] = __uint_as_float(r0[j]);
-        v[32 + j] = __uint_as_float(r1[j]);
+        v[j] = fmaf(__uint_as_float(r0[j]), e.alpha, bb[j]);
+        v[32 + j] = fmaf(__uint_as_float(r1[j]), e.alpha, bb[32 + j]);
       }
-      if (m < g.M) epilogue_64<EPI, OUT_F32>(v, m, n_base, g);
+      if (valid) epilogue_64<EPI, OUT_F32>(v, rm, n_base, g);
+      if (ci + 1 < CHUNKS) load_f4_batch<16>(e.bias, n_base + 64, g.N, bb);  // next chunk's bias
+      if (wait_clk) {
+        wait_clk[1] += c2 - c1;
+        wait_clk[2] += clock64() - c2;
+      }
     }
   }
   return true;

@@ -95,8 +95,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int num_tiles = g.tiles_m * g.tiles_n;
   const int KB = g.k_blocks;
 
-  if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
+  if (warp == 0 && lane == 0) {
+    // ------------------------------ TMA producer (one thread) ------------------
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -105,31 +105,39 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int n0 = (tile % g.tiles_n) * BN;
       for (int kb = 0; kb < KB; ++kb) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1, wc, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
-        if (lane == 0) {
+        {
           uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
           mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
           tma_load_2d(sa, &tmA, &full_bar[stage], kb * ELEMS_PER_STAGE, m0);
           tma_load_2d(sa + A_STAGE_BYTES, &tmW, &full_bar[stage], kb * ELEMS_PER_STAGE, n0);
         }
-        __syncwarp();
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer --------------------------------
+  } else if (warp == 1 && lane == 0) {
+    // ------------------------------ MMA issuer (one thread) --------------------
     int stage = 0;
     uint32_t phase = 0;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    bool stage_ready = false;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, wc, DEV_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
       for (int kb = 0; kb < KB; ++kb) {
-        if (!mbar_wait(&full_bar[stage], phase, wc, DEV_TIMEOUT_FULL)) { ok = false; break; }
+        // readiness of this stage was tested while the previous stage's MMAs
+        // were being issued; block only if that early test failed
+        if (!stage_ready) {
+          if (!mbar_wait(&full_bar[stage], phase, wc, DEV_TIMEOUT_FULL)) { ok = false; break; }
+        }
+        int ns = stage + 1;
+        uint32_t np = phase;
+        if (ns == STAGES) { ns = 0; np ^= 1; }
+        const uint32_t next_ready = mbar_test_wait(&full_bar[ns], np);
         tc_fence_after_sync();
-        if (lane == 0) {
+        {
           const uint32_t a_addr = smem_u32(smem + stage * Cfg::STAGE_BYTES);
           const uint32_t b_addr = a_addr + A_STAGE_BYTES;
           const uint64_t a_desc = make_smem_desc_sw128(a_addr, 16, 1024);
@@ -145,13 +153,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           mma_commit(&empty_bar[stage]);
           if (kb == KB - 1) mma_commit(&tfull_bar[acc]);
         }
-        __syncwarp();
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        stage = ns;
+        phase = np;
+        stage_ready = next_ready != 0;
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
-  } else {
+  } else if (warp >= 2) {
     // ------------------------------ epilogue ----------------------------------
     // Eight warps: warp w may read TMEM lanes [32 (w % 4), +32); warps 2-5 take
     // the first half of the tile's columns, warps 6-9 the second half.
@@ -380,6 +389,11 @@ int launch_gemm(const void* A, long lda, const void* W, long ldw, int operand_dt
   g.tiles_n = (N + BN - 1) / BN;
   g.epi = epi;
   g.status = dev_status;
+  {
+    const long esz = epi.out_f32 ? 4 : 2;
+    g.wide_store = (N % 16 == 0) && ((epi.ldo * esz) % 32 == 0) &&
+                   ((reinterpret_cast<uintptr_t>(epi.out) & 31) == 0);
+  }
 
   CUtensorMap tmA, tmW;
   int rc = encode_tmap_2d(&tmA, A, eb, (uint64_t)K, (uint64_t)M, (uint64_t)lda * eb,
