@@ -151,6 +151,32 @@ SD3_API int sd3_patch_embed(const void* latent, int io_dtype, const void* w_nk_b
                     const float* pos_table, float* out, void* scratch_bf16, int B, int C, int H,
                     int W, int patch, int E, void* stream);
 
+/* Patch embedding without any allocation and without a caller-provided
+ * scratch buffer.  It has no counterpart in the reference (whose
+ * PatchEmbedding, modules.cpp:1093-1117, allocates its temporaries with new[]).
+ *
+ * Who needs it: callers that cannot call cudaMalloc at the point where they
+ * run the operator -- e.g. while a stream is being captured into a CUDA graph
+ * (allocation is not allowed during capture), inside latency-critical serving
+ * loops (cudaMalloc/cudaFree synchronise the device), or under a host that
+ * fixes the memory budget when the library is loaded.
+ *
+ * Same arguments and result as sd3_patch_embed minus `scratch`: the gathered
+ * patches go to a fixed array of SD3_STATIC_PATCH_ELEMS bf16 elements (8 MiB)
+ * that is part of the library image on every GPU that loads it.  Calls with
+ * B * (H/patch) * (W/patch) * C * patch * patch above that limit fail with
+ * SD3_ERR_UNSUPPORTED.  The array is shared by all calls on a device and keeps
+ * the previous call's contents (none of which is read before being rewritten);
+ * calls whose GPU work overlaps race on it and must be serialised by the
+ * caller.  The first call on a device resolves the array's device address;
+ * issue that first call before any stream capture.  No cudaMalloc, cudaFree
+ * or allocating library routine is called, and no device status word is
+ * attached (bounded waits still apply). */
+#define SD3_STATIC_PATCH_ELEMS (4L * 1024 * 1024)
+SD3_API int sd3_patch_embed_static(const void* latent, int io_dtype, const void* w_nk_bf16,
+                                   const float* bias, const float* pos_table, float* out, int B,
+                                   int C, int H, int W, int patch, int E, void* stream);
+
 /* (R, C) row-major of in_dtype -> (C, R) row-major of out_dtype.  Turns a
  * boundary weight (in, out) into the packed (out, in) form. */
 SD3_API int sd3_pack_weight(const void* w_in_out, int in_dtype, void* w_nk, int out_dtype, int in_features,

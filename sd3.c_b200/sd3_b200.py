@@ -67,6 +67,7 @@ PROTOTYPES = {
     "sd3_sinusoidal_embedding": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "sd3_pos_embed_table": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "sd3_patch_embed": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "sd3_patch_embed_static": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "sd3_pack_weight": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
     "sd3_cast": (c_int, [c_void_p, c_int, c_void_p, c_int, c_long, c_void_p]),
     "sd3_rmsnorm_heads": (c_int, [c_void_p, c_int, c_long, c_long, c_int, c_int, c_int, c_void_p, c_float, c_void_p]),
@@ -278,6 +279,23 @@ def patch_embed(latent, w_nk_bf16, bias, pos_table, patch, E):
     check(lib().sd3_patch_embed(ptr(latent), dtype_tag(latent), ptr(w_nk_bf16), ptr(bias),
                                 ptr(pos_table), ptr(out), ptr(scratch), B, C, H, W, patch, E,
                                 stream_ptr()), "sd3_patch_embed")
+    return out
+
+
+STATIC_PATCH_ELEMS = 4 * 1024 * 1024
+
+
+def patch_embed_static(latent, w_nk_bf16, bias, pos_table, patch, E, out=None):
+    """sd3_patch_embed_static: same result as patch_embed, scratch inside the library.
+    `out` may be preallocated so that the call itself allocates nothing at all."""
+    torch = _torch()
+    B, C, H, W = latent.shape
+    hp, wp = H // patch, W // patch
+    if out is None:
+        out = torch.empty((B * hp * wp, E), device=latent.device, dtype=torch.float32)
+    check(lib().sd3_patch_embed_static(ptr(latent), dtype_tag(latent), ptr(w_nk_bf16), ptr(bias),
+                                       ptr(pos_table), ptr(out), B, C, H, W, patch, E,
+                                       stream_ptr()), "sd3_patch_embed_static")
     return out
 
 
