@@ -224,6 +224,32 @@ def kernel_breakdown(torch, s, peaks):
     return out, joint
 
 
+def profile_step(torch, s):
+    """One full denoiser step of the benchmark workload between
+    cudaProfilerStart/Stop, after one warm-up step (use a profiler's
+    "profile from start off" mode to capture just that step's launch list)."""
+    from oracle import mmdit_oracle as O
+    dev = torch.device("cuda", 0)
+    params = device_params(torch, O, dev, seed=2)
+    model = s.Model(24, range(13), 2048, 4096, 16, E, NH, 4, 2, 384, 128, True, s.PRECISION_BF16)
+    model.load(params)
+    gen = torch.Generator(device=dev).manual_seed(2)
+    latent = torch.randn(B, 16, HW, HW, generator=gen, device=dev).bfloat16()
+    captions = torch.randn(B, TC, 4096, generator=gen, device=dev).bfloat16()
+    pooled = torch.randn(B, 2048, generator=gen, device=dev).bfloat16()
+    tsteps = torch.rand(B, generator=gen, device=dev) * 1000
+    out = torch.empty_like(latent)
+    model.forward(pooled, captions, latent, tsteps, out)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    s.lib().sd3_launch_count(1)
+    model.forward(pooled, captions, latent, tsteps, out)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    s.assert_healthy()
+    print(json.dumps({"profile_case": "step", "launches": int(s.lib().sd3_launch_count(0))}))
+
+
 def profile_case(name, reps=3):
     """Runs ONE hot kernel a few times at a reduced size (inputs above L2, well
     under 2 GB) so that a profiler capture of it ends quickly.  Cases:
@@ -232,6 +258,8 @@ def profile_case(name, reps=3):
     s = load_binding()
     dev = "cuda"
     torch.manual_seed(0)
+    if name == "step":
+        return profile_step(torch, s)
     Bp = 2
     M = Bp * TX
     if name.startswith("gemm"):

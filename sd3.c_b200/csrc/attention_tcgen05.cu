@@ -21,6 +21,10 @@
 // fused_unpermute_split (cuda/dit.cu:475-545): the epilogue writes (B, T, E)
 // rows straight into the context and image output buffers.
 #include <cuda.h>
+#include <stdio.h>
+#include <stdlib.h>
+
+#include <vector>
 
 #include "kernels.h"
 #include "ptx.cuh"
@@ -52,6 +56,7 @@ struct AttnArgs {
   bf16* out_x;
   float scale_log2e;
   int* status;
+  long long* probe;  // diagnostics (SD3_ATTN_PROBE=1): 8 counters per CTA, else null
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -176,6 +181,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
       bool ok = mbar_wait(q_full, 0, wc, DEV_TIMEOUT_ATTN_Q);
       if (ok) ok = issue_s(0, false);
       if (ok && nsub > 1) ok = issue_s(1, false);
+      long long w_p = 0;
+      const long long t_mma0 = a.probe ? clock64() : 0;
       for (int t = 0; t < nsub && ok; ++t) {
         const int j = t >> 1, st = j % AT_STAGES;
         // While P_t is still being produced, test the barriers the next issues
@@ -187,7 +194,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
           k_ready = mbar_test_wait(&k_full[j2 % AT_STAGES], (j2 / AT_STAGES) & 1);
         }
         // O += P_t V_t
+        const long long cp0 = a.probe ? clock64() : 0;
         if (!mbar_wait(&p_ready[t & 1], (t >> 1) & 1, wc, DEV_TIMEOUT_ATTN_P)) break;
+        if (a.probe) w_p += clock64() - cp0;
         if (!v_ready) {
           if (!mbar_wait(&v_full[st], (j / AT_STAGES) & 1, wc, DEV_TIMEOUT_ATTN_KV)) break;
         }
@@ -208,6 +217,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
         // tensor pipe executes in issue order): refill it with S_{t+2}
         if (t + 2 < nsub) ok = issue_s(t + 2, k_ready != 0);
       }
+      if (a.probe) {
+        const long cta = (static_cast<long>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+        a.probe[cta * 8 + 0] = clock64() - t_mma0;
+        a.probe[cta * 8 + 1] = w_p;
+      }
     }
   } else {
     // ------------------------------ softmax + epilogue ------------------------
@@ -221,15 +235,21 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
     bool ok = true;
     bool fetched = false;  // scores of sub-tile t already requested from TMEM
     uint32_t r0[32], r1[32];
+    long long w_s = 0, w_ld = 0, t_math = 0, w_st = 0, n_miss = 0;
+    const long long t_sm0 = a.probe ? clock64() : 0;
     for (int t = 0; t < nsub; ++t) {
       const uint32_t s_tmem = lane_base + AT_S_COL + (t & 1) * AT_SUB;
+      const long long c0 = a.probe ? clock64() : 0;
       if (!fetched) {
+        ++n_miss;
         if (!mbar_wait_warp(&s_full[t & 1], (t >> 1) & 1, wc, DEV_TIMEOUT_ATTN_S)) { ok = false; break; }
         tc_fence_after_sync();
         tmem_ld_32x32b_x32(s_tmem, r0);
         tmem_ld_32x32b_x32(s_tmem + 32, r1);
       }
+      const long long c1 = a.probe ? clock64() : 0;
       tmem_wait_ld();
+      const long long c2 = a.probe ? clock64() : 0;
       const int kv0 = t * AT_SUB;
       if (kv0 + AT_SUB > T) {  // ragged last sub-tile: keys >= T do not exist
 #pragma unroll
@@ -292,6 +312,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
       }
       tmem_st_32x32b_x32(s_tmem, pk);
       l += ls0 + ls1;
+      const long long c3 = a.probe ? clock64() : 0;
       // If the next scores are already there (they normally are: S is issued one
       // sub-tile ahead), request them now so the TMEM load overlaps the hand-off.
       fetched = false;
@@ -311,6 +332,21 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[t & 1]);
+      if (a.probe) {
+        w_s += c1 - c0;
+        w_ld += c2 - c1;
+        t_math += c3 - c2;
+        w_st += clock64() - c3;
+      }
+    }
+    if (a.probe && warp == 2 && lane == 0) {
+      const long cta = (static_cast<long>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+      a.probe[cta * 8 + 2] = clock64() - t_sm0;
+      a.probe[cta * 8 + 3] = w_s;
+      a.probe[cta * 8 + 4] = w_ld;
+      a.probe[cta * 8 + 5] = t_math;
+      a.probe[cta * 8 + 6] = w_st;
+      a.probe[cta * 8 + 7] = n_miss;
     }
     if (ok && mbar_wait_warp(o_full, 0, wc, DEV_TIMEOUT_ATTN_O)) {
       tc_fence_after_sync();
@@ -395,9 +431,39 @@ int launch_attention_bf16(const bf16* qkv, int B, int T, int NH, int Tc, bf16* o
   a.out_c = out_c; a.out_x = out_x;
   a.scale_log2e = scale * 1.4426950408889634f;
   a.status = dev_status;
+  a.probe = nullptr;
   const dim3 grid((T + AT_BM - 1) / AT_BM, NH, B);
+  // Diagnostic: SD3_ATTN_PROBE=1 makes every launch synchronous and prints where
+  // the MMA thread and a softmax warp spent their cycles (averages over CTAs).
+  static const bool probing = []() {
+    const char* v = getenv("SD3_ATTN_PROBE");
+    return v && v[0] == '1';
+  }();
+  const long nctas = static_cast<long>(grid.x) * grid.y * grid.z;
+  if (probing && dev_status) {
+    if (cudaMalloc(&a.probe, sizeof(long long) * 8 * nctas) != cudaSuccess) a.probe = nullptr;
+    if (a.probe) cudaMemset(a.probe, 0, sizeof(long long) * 8 * nctas);
+  }
   attention_tcgen05_kernel<<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(tm, a);
-  return after_launch("attention_tcgen05_kernel");
+  const int lrc = after_launch("attention_tcgen05_kernel");
+  if (a.probe) {
+    std::vector<long long> hbuf(8 * nctas);
+    cudaStreamSynchronize(stream);
+    cudaMemcpy(hbuf.data(), a.probe, hbuf.size() * sizeof(long long), cudaMemcpyDeviceToHost);
+    cudaFree(a.probe);
+    double sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (long cidx = 0; cidx < nctas; ++cidx)
+      for (int i = 0; i < 8; ++i) sum[i] += static_cast<double>(hbuf[cidx * 8 + i]);
+    const int nsub = (T + AT_SUB - 1) / AT_SUB;
+    fprintf(stderr,
+            "[attention probe] B %d T %d NH %d (%d sub-tiles): per sub-tile: mma thread %.0f clk (waiting P %.0f); "
+            "softmax warp %.0f clk: wait S %.0f, wait TMEM load %.0f, math %.0f, store+handoff %.0f; "
+            "scores not prefetched in %.1f%% of sub-tiles\n",
+            B, T, NH, nsub, sum[0] / nctas / nsub, sum[1] / nctas / nsub, sum[2] / nctas / nsub,
+            sum[3] / nctas / nsub, sum[4] / nctas / nsub, sum[5] / nctas / nsub, sum[6] / nctas / nsub,
+            100.0 * sum[7] / nctas / nsub);
+  }
+  return lrc;
 }
 
 }  // namespace sd3
