@@ -252,6 +252,16 @@ SD3_API int sd3_dit_forward(sd3_model* m, const void* pooled, const void* captio
 SD3_API int sd3_block_forward(sd3_model* m, int layer, const float* y, float* c, float* x, int B, int Tc,
                       int Tx, void* stream);
 
+/* One sampling-loop update after a denoiser call on the stacked batch
+ * [conditional; unconditional]: v = v_u + guidance (v_c - v_u),
+ * x_state += dsigma * v (fp32 master copy, half_elems elements), and the new
+ * latent is written to BOTH halves of x_stacked (2 * half_elems elements of
+ * io_dtype) so it is the next step's model input.  v_stacked is the denoiser
+ * output for x_stacked.  The reference has no sampler (README.md:1-7); this is
+ * the caller next to DiT_forward. */
+SD3_API int sd3_cfg_euler_step(float* x_state, void* x_stacked, const void* v_stacked, int io_dtype,
+                               long half_elems, float guidance, float dsigma, void* stream);
+
 /* Number of kernels this library launched since the last call with reset != 0
  * (process-wide counter, for benchmarks). */
 SD3_API long sd3_launch_count(int reset);

@@ -276,3 +276,29 @@ def random_params(shapes, seed, std=0.02, dtype=torch.float32, device="cpu", bia
 SD35_MEDIUM = dict(num_layers=24, dual_layers=tuple(range(13)), in_dim=16, E=1536, pooled_dim=2048,
                    captions_dim=4096, patch=2, attn_heads=24, mlp_expand=4, pos_max=384,
                    base_height=128)
+
+
+def sigma_schedule(steps, shift=3.0):
+    """Shifted flow-matching sigmas used by the sampling-loop checks:
+    s = shift*u/(1+(shift-1)*u), u = 1 - i/steps, then a final 0.  The reference
+    has no sampler, so this schedule is pinned by nothing in the reference; the
+    loop is checked step for step against this restatement only."""
+    sig = [shift * (1.0 - i / steps) / (1.0 + (shift - 1.0) * (1.0 - i / steps)) for i in range(steps)]
+    return sig + [0.0]
+
+
+def sample_loop(latents, cond_captions, cond_pooled, uncond_captions, uncond_pooled, p, cfg, steps,
+                guidance=4.5, shift=3.0):
+    """Euler flow-matching sampling with classifier-free guidance around
+    dit_forward: x <- x + (s_{i+1} - s_i) (v_u + g (v_c - v_u)), t = 1000 s_i."""
+    x = latents.clone()
+    sig = sigma_schedule(steps, shift)
+    n = x.shape[0]
+    for i in range(steps):
+        t = torch.full((n,), 1000.0 * sig[i])
+        args = (p, cfg["num_layers"], cfg["dual_attention_layers"], cfg["attn_heads"], cfg["patch_size"],
+                cfg["pos_embed_max_size"], cfg["base_height"], True)
+        vc = dit_forward(cond_pooled, cond_captions, x, t, *args)
+        vu = dit_forward(uncond_pooled, uncond_captions, x, t, *args)
+        x = x + (sig[i + 1] - sig[i]) * (vu + guidance * (vc - vu))
+    return x

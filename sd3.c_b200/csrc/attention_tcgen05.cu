@@ -46,8 +46,9 @@ constexpr int AT_TILE_BYTES = AT_BN * AT_D * 2;  // 16 KiB
 constexpr int AT_SUB_BYTES = AT_SUB * AT_D * 2;  // 8 KiB
 constexpr int AT_THREADS = 192;
 constexpr int AT_TMEM_COLS = 256;
-constexpr int AT_S_COL = 0;     // two score buffers of 64 fp32 columns: [0,64) and [64,128)
-constexpr int AT_O_COL = 128;   // O: 64 fp32 columns
+constexpr int AT_NBUF = 3;      // score buffers of 64 fp32 columns: [0,64), [64,128), [128,192)
+constexpr int AT_S_COL = 0;
+constexpr int AT_O_COL = 192;   // O: 64 fp32 columns
 constexpr int AT_SMEM_BYTES = (1 + 2 * AT_STAGES) * AT_TILE_BYTES + 256 + 1024;
 
 struct AttnArgs {
@@ -84,9 +85,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
   uint64_t* v_full = k_full + AT_STAGES;    // AT_STAGES
   uint64_t* k_empty = v_full + AT_STAGES;   // AT_STAGES
   uint64_t* v_empty = k_empty + AT_STAGES;  // AT_STAGES
-  uint64_t* s_full = v_empty + AT_STAGES;   // 2 (one per score buffer)
-  uint64_t* p_ready = s_full + 2;           // 2
-  uint64_t* pv_done = p_ready + 2;          // 1: one phase per P V product
+  uint64_t* s_full = v_empty + AT_STAGES;   // AT_NBUF (one per score buffer)
+  uint64_t* p_ready = s_full + AT_NBUF;     // AT_NBUF
+  uint64_t* pv_done = p_ready + AT_NBUF;    // 1: one phase per P V product
   uint64_t* o_full = pv_done + 1;           // 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
   int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
@@ -107,7 +108,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
       mbar_init(&k_empty[s], 1);
       mbar_init(&v_empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < AT_NBUF; ++s) {
       mbar_init(&s_full[s], 1);
       mbar_init(&p_ready[s], 4);
     }
@@ -166,13 +167,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
         if (!mbar_wait(&k_full[st], (j / AT_STAGES) & 1, wc, DEV_TIMEOUT_ATTN_KV)) return false;
       }
       tc_fence_after_sync();
-      const uint32_t s_tmem = tmem_base + AT_S_COL + (u & 1) * AT_SUB;
+      const uint32_t s_tmem = tmem_base + AT_S_COL + (u % AT_NBUF) * AT_SUB;
       const uint64_t k_desc = make_smem_desc_sw128(
           smem_u32(k_smem + st * AT_TILE_BYTES + (u & 1) * AT_SUB_BYTES), 16, 1024);
 #pragma unroll
       for (int k = 0; k < AT_D / 16; ++k)
         mma_f16_ss(s_tmem, q_desc + 2 * k, k_desc + 2 * k, IDESC_S, k != 0);
-      mma_commit(&s_full[u & 1]);
+      mma_commit(&s_full[u % AT_NBUF]);
       if ((u & 1) == 1 || u == nsub - 1) mma_commit(&k_empty[st]);
       return true;
     };
@@ -195,27 +196,42 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
         }
         // O += P_t V_t
         const long long cp0 = a.probe ? clock64() : 0;
-        if (!mbar_wait(&p_ready[t & 1], (t >> 1) & 1, wc, DEV_TIMEOUT_ATTN_P)) break;
+        if (!mbar_wait(&p_ready[t % AT_NBUF], (t / AT_NBUF) & 1, wc, DEV_TIMEOUT_ATTN_P)) break;
         if (a.probe) w_p += clock64() - cp0;
         if (!v_ready) {
           if (!mbar_wait(&v_full[st], (j / AT_STAGES) & 1, wc, DEV_TIMEOUT_ATTN_KV)) break;
         }
+        // O += P_t V_t and S_{t+2} = Q K_{t+2}^T are independent accumulation
+        // chains (three score buffers: S_{t+2} does not touch the buffer P_t
+        // lives in), so their MMAs are issued interleaved and each chain's
+        // accumulate-to-accumulate latency hides behind the other.
+        const int u = t + 2;
+        const bool do_s = u < nsub;
+        const int j2 = u >> 1, st2 = j2 % AT_STAGES;
+        if (do_s && (u & 1) == 0 && !k_ready) {
+          if (!mbar_wait(&k_full[st2], (j2 / AT_STAGES) & 1, wc, DEV_TIMEOUT_ATTN_KV)) break;
+        }
         tc_fence_after_sync();
-        const uint32_t p_tmem = tmem_base + AT_S_COL + (t & 1) * AT_SUB;
+        const uint32_t p_tmem = tmem_base + AT_S_COL + (t % AT_NBUF) * AT_SUB;
         const uint64_t v_desc = make_smem_desc_sw128(
             smem_u32(v_smem + st * AT_TILE_BYTES + (t & 1) * AT_SUB_BYTES), 1024, 1024);
+        const uint32_t s_tmem2 = tmem_base + AT_S_COL + (u % AT_NBUF) * AT_SUB;
+        const uint64_t k_desc2 = make_smem_desc_sw128(
+            smem_u32(k_smem + st2 * AT_TILE_BYTES + (u & 1) * AT_SUB_BYTES), 16, 1024);
 #pragma unroll
         for (int k = 0; k < AT_SUB / 16; ++k) {
           // 16 keys: 8 TMEM columns of packed bf16 pairs; 16 rows of V (128 B each)
           mma_f16_ts(o_tmem, p_tmem + 8 * k, v_desc + static_cast<uint64_t>((k * 16 * 128) >> 4),
                      IDESC_O, (t | k) != 0);
+          if (do_s) mma_f16_ss(s_tmem2, q_desc + 2 * k, k_desc2 + 2 * k, IDESC_S, k != 0);
         }
         mma_commit(pv_done);
         if ((t & 1) == 1 || t == nsub - 1) mma_commit(&v_empty[st]);
         if (t == nsub - 1) mma_commit(o_full);
-        // the buffer of P_t is free once that product has been issued (the
-        // tensor pipe executes in issue order): refill it with S_{t+2}
-        if (t + 2 < nsub) ok = issue_s(t + 2, k_ready != 0);
+        if (do_s) {
+          mma_commit(&s_full[u % AT_NBUF]);
+          if ((u & 1) == 1 || u == nsub - 1) mma_commit(&k_empty[st2]);
+        }
       }
       if (a.probe) {
         const long cta = (static_cast<long>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
@@ -238,11 +254,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
     long long w_s = 0, w_ld = 0, t_math = 0, w_st = 0, n_miss = 0;
     const long long t_sm0 = a.probe ? clock64() : 0;
     for (int t = 0; t < nsub; ++t) {
-      const uint32_t s_tmem = lane_base + AT_S_COL + (t & 1) * AT_SUB;
+      const uint32_t s_tmem = lane_base + AT_S_COL + (t % AT_NBUF) * AT_SUB;
       const long long c0 = a.probe ? clock64() : 0;
       if (!fetched) {
         ++n_miss;
-        if (!mbar_wait_warp(&s_full[t & 1], (t >> 1) & 1, wc, DEV_TIMEOUT_ATTN_S)) { ok = false; break; }
+        if (!mbar_wait_warp(&s_full[t % AT_NBUF], (t / AT_NBUF) & 1, wc, DEV_TIMEOUT_ATTN_S)) { ok = false; break; }
         tc_fence_after_sync();
         tmem_ld_32x32b_x32(s_tmem, r0);
         tmem_ld_32x32b_x32(s_tmem + 32, r1);
@@ -318,11 +334,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
       fetched = false;
       if (t + 1 < nsub) {
         uint32_t rdy = 0;
-        if (lane == 0) rdy = mbar_test_wait(&s_full[(t + 1) & 1], ((t + 1) >> 1) & 1);
+        if (lane == 0) rdy = mbar_test_wait(&s_full[(t + 1) % AT_NBUF], ((t + 1) / AT_NBUF) & 1);
         rdy = __shfl_sync(0xffffffffu, rdy, 0);
         if (rdy) {
           tc_fence_after_sync();
-          const uint32_t s_next = lane_base + AT_S_COL + ((t + 1) & 1) * AT_SUB;
+          const uint32_t s_next = lane_base + AT_S_COL + ((t + 1) % AT_NBUF) * AT_SUB;
           tmem_ld_32x32b_x32(s_next, r0);
           tmem_ld_32x32b_x32(s_next + 32, r1);
           fetched = true;
@@ -331,7 +347,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_ready[t & 1]);
+      if (lane == 0) mbar_arrive(&p_ready[t % AT_NBUF]);
       if (a.probe) {
         w_s += c1 - c0;
         w_ld += c2 - c1;

@@ -23,7 +23,7 @@ namespace {
 // LayerNorm + modulate.  One warp per row, the row lives in registers.
 // ----------------------------------------------------------------------------
 template <int MAXV, bool OUT_F32, bool DUAL>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 ln_modulate_kernel(const float* __restrict__ x, long rows, int T, int E, float eps,
                    const float* __restrict__ shift1, const float* __restrict__ scale1,
                    void* __restrict__ out1, const float* __restrict__ shift2,

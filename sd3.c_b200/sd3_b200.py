@@ -78,6 +78,7 @@ PROTOTYPES = {
     "sd3_model_reserve": (c_int, [c_void_p, c_int, c_int, c_int, c_int]),
     "sd3_dit_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "sd3_block_forward": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "sd3_cfg_euler_step": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_long, c_float, c_float, c_void_p]),
     "sd3_launch_count": (c_long, [c_int]),
 }
 
@@ -383,3 +384,44 @@ def shard_range(n, world, rank):
     base, rem = divmod(n, world)
     lo = rank * base + min(rank, rem)
     return lo, lo + base + (1 if rank < rem else 0)
+
+
+# ---------------------------------------------------------------------------
+# sampling loop (the caller next to the denoiser; the reference has none)
+# ---------------------------------------------------------------------------
+def sigma_schedule(steps, shift=3.0):
+    """Flow-matching sigmas: s_i = shift * u / (1 + (shift - 1) * u) with
+    u = 1 - i/steps for i = 0..steps-1, followed by a final 0.
+    The model is called at timestep t = 1000 * sigma."""
+    out = []
+    for i in range(steps):
+        u = 1.0 - i / steps
+        out.append(shift * u / (1.0 + (shift - 1.0) * u))
+    out.append(0.0)
+    return out
+
+
+def sample(model, latents, cond_captions, cond_pooled, uncond_captions, uncond_pooled, steps=28,
+           guidance=4.5, shift=3.0):
+    """Euler flow-matching sampling with classifier-free guidance.  Conditional
+    and unconditional branches run stacked in one denoiser call per step
+    (effective batch 2n); the update and the refresh of the stacked input are
+    one fused kernel (sd3_cfg_euler_step).  Returns the final latents (n, C, H, W)
+    in float32."""
+    torch = _torch()
+    n = latents.shape[0]
+    dt = latents.dtype
+    x_state = latents.to(torch.float32).contiguous().clone()
+    x2 = torch.cat([latents, latents], 0).contiguous()
+    caps = torch.cat([cond_captions, uncond_captions], 0).to(dt).contiguous()
+    pooled = torch.cat([cond_pooled, uncond_pooled], 0).to(dt).contiguous()
+    v = torch.empty_like(x2)
+    sig = sigma_schedule(steps, shift)
+    tvec = torch.empty(2 * n, device=latents.device, dtype=torch.float32)
+    half = x_state.numel()
+    for i in range(steps):
+        tvec.fill_(1000.0 * sig[i])
+        model.forward(pooled, caps, x2, tvec, v)
+        check(lib().sd3_cfg_euler_step(ptr(x_state), ptr(x2), ptr(v), dtype_tag(x2), half, guidance,
+                                       sig[i + 1] - sig[i], stream_ptr()), "sd3_cfg_euler_step")
+    return x_state
