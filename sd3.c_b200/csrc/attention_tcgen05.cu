@@ -87,8 +87,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
   uint64_t* v_empty = k_empty + AT_STAGES;  // AT_STAGES
   uint64_t* s_full = v_empty + AT_STAGES;   // AT_NBUF (one per score buffer)
   uint64_t* p_ready = s_full + AT_NBUF;     // AT_NBUF
-  uint64_t* pv_done = p_ready + AT_NBUF;    // 1: one phase per P V product
-  uint64_t* o_full = pv_done + 1;           // 1
+  uint64_t* pv_done = p_ready + AT_NBUF;    // 2: products of even / odd sub-tiles
+  uint64_t* o_full = pv_done + 2;           // 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
   int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
 
@@ -112,7 +112,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
       mbar_init(&s_full[s], 1);
       mbar_init(&p_ready[s], 4);
     }
-    mbar_init(pv_done, 1);
+    mbar_init(&pv_done[0], 1);
+    mbar_init(&pv_done[1], 1);
     mbar_init(o_full, 1);
     *s_abort = 0;
     fence_barrier_init();
@@ -182,18 +183,22 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
       bool ok = mbar_wait(q_full, 0, wc, DEV_TIMEOUT_ATTN_Q);
       if (ok) ok = issue_s(0, false);
       if (ok && nsub > 1) ok = issue_s(1, false);
-      long long w_p = 0;
+      long long w_p = 0, w_si = 0, w_pv = 0;
       const long long t_mma0 = a.probe ? clock64() : 0;
       for (int t = 0; t < nsub && ok; ++t) {
         const int j = t >> 1, st = j % AT_STAGES;
-        // While P_t is still being produced, test the barriers the next issues
-        // will need, so their latency is off the critical path.
-        uint32_t v_ready = 1, k_ready = 1;
-        if ((t & 1) == 0) v_ready = mbar_test_wait(&v_full[st], (j / AT_STAGES) & 1);
-        if (t + 2 < nsub && (t & 1) == 0) {
-          const int j2 = (t + 2) >> 1;
-          k_ready = mbar_test_wait(&k_full[j2 % AT_STAGES], (j2 / AT_STAGES) & 1);
+        // S_{t+2} does not depend on P_t: its buffer, (t+2) % 3, held P_{t-1},
+        // whose product was issued in the previous iteration (the tensor pipe
+        // executes in issue order).  Issue it first so the scores stay two
+        // sub-tiles ahead of the softmax.
+        const long long cs0 = a.probe ? clock64() : 0;
+        if (t + 2 < nsub) {
+          ok = issue_s(t + 2, false);
+          if (!ok) break;
         }
+        if (a.probe) w_si += clock64() - cs0;
+        uint32_t v_ready = 1;
+        if ((t & 1) == 0) v_ready = mbar_test_wait(&v_full[st], (j / AT_STAGES) & 1);
         // O += P_t V_t
         const long long cp0 = a.probe ? clock64() : 0;
         if (!mbar_wait(&p_ready[t % AT_NBUF], (t / AT_NBUF) & 1, wc, DEV_TIMEOUT_ATTN_P)) break;
@@ -201,42 +206,28 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
         if (!v_ready) {
           if (!mbar_wait(&v_full[st], (j / AT_STAGES) & 1, wc, DEV_TIMEOUT_ATTN_KV)) break;
         }
-        // O += P_t V_t and S_{t+2} = Q K_{t+2}^T are independent accumulation
-        // chains (three score buffers: S_{t+2} does not touch the buffer P_t
-        // lives in), so their MMAs are issued interleaved and each chain's
-        // accumulate-to-accumulate latency hides behind the other.
-        const int u = t + 2;
-        const bool do_s = u < nsub;
-        const int j2 = u >> 1, st2 = j2 % AT_STAGES;
-        if (do_s && (u & 1) == 0 && !k_ready) {
-          if (!mbar_wait(&k_full[st2], (j2 / AT_STAGES) & 1, wc, DEV_TIMEOUT_ATTN_KV)) break;
-        }
+        const long long cv0 = a.probe ? clock64() : 0;
         tc_fence_after_sync();
         const uint32_t p_tmem = tmem_base + AT_S_COL + (t % AT_NBUF) * AT_SUB;
         const uint64_t v_desc = make_smem_desc_sw128(
             smem_u32(v_smem + st * AT_TILE_BYTES + (t & 1) * AT_SUB_BYTES), 1024, 1024);
-        const uint32_t s_tmem2 = tmem_base + AT_S_COL + (u % AT_NBUF) * AT_SUB;
-        const uint64_t k_desc2 = make_smem_desc_sw128(
-            smem_u32(k_smem + st2 * AT_TILE_BYTES + (u & 1) * AT_SUB_BYTES), 16, 1024);
 #pragma unroll
         for (int k = 0; k < AT_SUB / 16; ++k) {
           // 16 keys: 8 TMEM columns of packed bf16 pairs; 16 rows of V (128 B each)
           mma_f16_ts(o_tmem, p_tmem + 8 * k, v_desc + static_cast<uint64_t>((k * 16 * 128) >> 4),
                      IDESC_O, (t | k) != 0);
-          if (do_s) mma_f16_ss(s_tmem2, q_desc + 2 * k, k_desc2 + 2 * k, IDESC_S, k != 0);
         }
-        mma_commit(pv_done);
+        mma_commit(&pv_done[t & 1]);
         if ((t & 1) == 1 || t == nsub - 1) mma_commit(&v_empty[st]);
         if (t == nsub - 1) mma_commit(o_full);
-        if (do_s) {
-          mma_commit(&s_full[u % AT_NBUF]);
-          if ((u & 1) == 1 || u == nsub - 1) mma_commit(&k_empty[st2]);
-        }
+        if (a.probe) w_pv += clock64() - cv0;
       }
       if (a.probe) {
         const long cta = (static_cast<long>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-        a.probe[cta * 8 + 0] = clock64() - t_mma0;
-        a.probe[cta * 8 + 1] = w_p;
+        a.probe[cta * 12 + 0] = clock64() - t_mma0;
+        a.probe[cta * 12 + 1] = w_p;
+        a.probe[cta * 12 + 8] = w_si;
+        a.probe[cta * 12 + 9] = w_pv;
       }
     }
   } else {
@@ -296,7 +287,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
           }
           // P_{t-1} V_{t-1} must have landed in O before O is rescaled; the
           // product of this sub-tile is only issued after p_ready below.
-          if (!mbar_wait_warp(pv_done, (t - 1) & 1, wc, DEV_TIMEOUT_ATTN_O)) { ok = false; break; }
+          if (!mbar_wait_warp(&pv_done[(t - 1) & 1], ((t - 1) >> 1) & 1, wc, DEV_TIMEOUT_ATTN_O)) { ok = false; break; }
           tc_fence_after_sync();
           uint32_t o0[32];
           tmem_ld_32x32b_x32(o_tmem, o0);
@@ -357,12 +348,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
     }
     if (a.probe && warp == 2 && lane == 0) {
       const long cta = (static_cast<long>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-      a.probe[cta * 8 + 2] = clock64() - t_sm0;
-      a.probe[cta * 8 + 3] = w_s;
-      a.probe[cta * 8 + 4] = w_ld;
-      a.probe[cta * 8 + 5] = t_math;
-      a.probe[cta * 8 + 6] = w_st;
-      a.probe[cta * 8 + 7] = n_miss;
+      a.probe[cta * 12 + 2] = clock64() - t_sm0;
+      a.probe[cta * 12 + 3] = w_s;
+      a.probe[cta * 12 + 4] = w_ld;
+      a.probe[cta * 12 + 5] = t_math;
+      a.probe[cta * 12 + 6] = w_st;
+      a.probe[cta * 12 + 7] = n_miss;
     }
     if (ok && mbar_wait_warp(o_full, 0, wc, DEV_TIMEOUT_ATTN_O)) {
       tc_fence_after_sync();
@@ -457,25 +448,26 @@ int launch_attention_bf16(const bf16* qkv, int B, int T, int NH, int Tc, bf16* o
   }();
   const long nctas = static_cast<long>(grid.x) * grid.y * grid.z;
   if (probing && dev_status) {
-    if (cudaMalloc(&a.probe, sizeof(long long) * 8 * nctas) != cudaSuccess) a.probe = nullptr;
-    if (a.probe) cudaMemset(a.probe, 0, sizeof(long long) * 8 * nctas);
+    if (cudaMalloc(&a.probe, sizeof(long long) * 12 * nctas) != cudaSuccess) a.probe = nullptr;
+    if (a.probe) cudaMemset(a.probe, 0, sizeof(long long) * 12 * nctas);
   }
   attention_tcgen05_kernel<<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(tm, a);
   const int lrc = after_launch("attention_tcgen05_kernel");
   if (a.probe) {
-    std::vector<long long> hbuf(8 * nctas);
+    std::vector<long long> hbuf(12 * nctas);
     cudaStreamSynchronize(stream);
     cudaMemcpy(hbuf.data(), a.probe, hbuf.size() * sizeof(long long), cudaMemcpyDeviceToHost);
     cudaFree(a.probe);
-    double sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    double sum[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
     for (long cidx = 0; cidx < nctas; ++cidx)
-      for (int i = 0; i < 8; ++i) sum[i] += static_cast<double>(hbuf[cidx * 8 + i]);
+      for (int i = 0; i < 12; ++i) sum[i] += static_cast<double>(hbuf[cidx * 12 + i]);
     const int nsub = (T + AT_SUB - 1) / AT_SUB;
     fprintf(stderr,
-            "[attention probe] B %d T %d NH %d (%d sub-tiles): per sub-tile: mma thread %.0f clk (waiting P %.0f); "
+            "[attention probe] B %d T %d NH %d (%d sub-tiles): per sub-tile: mma thread %.0f clk (waiting P %.0f, issuing S %.0f, issuing PV %.0f); "
             "softmax warp %.0f clk: wait S %.0f, wait TMEM load %.0f, math %.0f, store+handoff %.0f; "
             "scores not prefetched in %.1f%% of sub-tiles\n",
-            B, T, NH, nsub, sum[0] / nctas / nsub, sum[1] / nctas / nsub, sum[2] / nctas / nsub,
+            B, T, NH, nsub, sum[0] / nctas / nsub, sum[1] / nctas / nsub, sum[8] / nctas / nsub,
+            sum[9] / nctas / nsub, sum[2] / nctas / nsub,
             sum[3] / nctas / nsub, sum[4] / nctas / nsub, sum[5] / nctas / nsub, sum[6] / nctas / nsub,
             100.0 * sum[7] / nctas / nsub);
   }
