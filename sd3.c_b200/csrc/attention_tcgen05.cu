@@ -60,6 +60,11 @@ struct AttnArgs {
   long long* probe;  // diagnostics (SD3_ATTN_PROBE=1): 8 counters per CTA, else null
 };
 
+// Cycle counters are compiled in only in the PROBE instantiation: even behind a
+// runtime flag they cost the softmax loop about a tenth of its throughput.
+#define ATX_PROBING (PROBE && a.probe != nullptr)
+#define ATX_CLK() ((PROBE && a.probe) ? clock64() : 0ll)
+
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -71,6 +76,7 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
+template <bool PROBE>
 __global__ void __launch_bounds__(AT_THREADS, 2)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -184,29 +190,29 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
       if (ok) ok = issue_s(0, false);
       if (ok && nsub > 1) ok = issue_s(1, false);
       long long w_p = 0, w_si = 0, w_pv = 0;
-      const long long t_mma0 = a.probe ? clock64() : 0;
+      const long long t_mma0 = ATX_CLK();
       for (int t = 0; t < nsub && ok; ++t) {
         const int j = t >> 1, st = j % AT_STAGES;
         // S_{t+2} does not depend on P_t: its buffer, (t+2) % 3, held P_{t-1},
         // whose product was issued in the previous iteration (the tensor pipe
         // executes in issue order).  Issue it first so the scores stay two
         // sub-tiles ahead of the softmax.
-        const long long cs0 = a.probe ? clock64() : 0;
+        const long long cs0 = ATX_CLK();
         if (t + 2 < nsub) {
           ok = issue_s(t + 2, false);
           if (!ok) break;
         }
-        if (a.probe) w_si += clock64() - cs0;
+        if (ATX_PROBING) w_si += clock64() - cs0;
         uint32_t v_ready = 1;
         if ((t & 1) == 0) v_ready = mbar_test_wait(&v_full[st], (j / AT_STAGES) & 1);
         // O += P_t V_t
-        const long long cp0 = a.probe ? clock64() : 0;
+        const long long cp0 = ATX_CLK();
         if (!mbar_wait(&p_ready[t % AT_NBUF], (t / AT_NBUF) & 1, wc, DEV_TIMEOUT_ATTN_P)) break;
-        if (a.probe) w_p += clock64() - cp0;
+        if (ATX_PROBING) w_p += clock64() - cp0;
         if (!v_ready) {
           if (!mbar_wait(&v_full[st], (j / AT_STAGES) & 1, wc, DEV_TIMEOUT_ATTN_KV)) break;
         }
-        const long long cv0 = a.probe ? clock64() : 0;
+        const long long cv0 = ATX_CLK();
         tc_fence_after_sync();
         const uint32_t p_tmem = tmem_base + AT_S_COL + (t % AT_NBUF) * AT_SUB;
         const uint64_t v_desc = make_smem_desc_sw128(
@@ -220,9 +226,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
         mma_commit(&pv_done[t & 1]);
         if ((t & 1) == 1 || t == nsub - 1) mma_commit(&v_empty[st]);
         if (t == nsub - 1) mma_commit(o_full);
-        if (a.probe) w_pv += clock64() - cv0;
+        if (ATX_PROBING) w_pv += clock64() - cv0;
       }
-      if (a.probe) {
+      if (ATX_PROBING) {
         const long cta = (static_cast<long>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
         a.probe[cta * 12 + 0] = clock64() - t_mma0;
         a.probe[cta * 12 + 1] = w_p;
@@ -243,10 +249,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
     bool fetched = false;  // scores of sub-tile t already requested from TMEM
     uint32_t r0[32], r1[32];
     long long w_s = 0, w_ld = 0, t_math = 0, w_st = 0, n_miss = 0;
-    const long long t_sm0 = a.probe ? clock64() : 0;
+    const long long t_sm0 = ATX_CLK();
     for (int t = 0; t < nsub; ++t) {
       const uint32_t s_tmem = lane_base + AT_S_COL + (t % AT_NBUF) * AT_SUB;
-      const long long c0 = a.probe ? clock64() : 0;
+      const long long c0 = ATX_CLK();
       if (!fetched) {
         ++n_miss;
         if (!mbar_wait_warp(&s_full[t % AT_NBUF], (t / AT_NBUF) & 1, wc, DEV_TIMEOUT_ATTN_S)) { ok = false; break; }
@@ -254,9 +260,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
         tmem_ld_32x32b_x32(s_tmem, r0);
         tmem_ld_32x32b_x32(s_tmem + 32, r1);
       }
-      const long long c1 = a.probe ? clock64() : 0;
+      const long long c1 = ATX_CLK();
       tmem_wait_ld();
-      const long long c2 = a.probe ? clock64() : 0;
+      const long long c2 = ATX_CLK();
       const int kv0 = t * AT_SUB;
       if (kv0 + AT_SUB > T) {  // ragged last sub-tile: keys >= T do not exist
 #pragma unroll
@@ -319,7 +325,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
       }
       tmem_st_32x32b_x32(s_tmem, pk);
       l += ls0 + ls1;
-      const long long c3 = a.probe ? clock64() : 0;
+      const long long c3 = ATX_CLK();
       // If the next scores are already there (they normally are: S is issued one
       // sub-tile ahead), request them now so the TMEM load overlaps the hand-off.
       fetched = false;
@@ -339,14 +345,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[t % AT_NBUF]);
-      if (a.probe) {
+      if (ATX_PROBING) {
         w_s += c1 - c0;
         w_ld += c2 - c1;
         t_math += c3 - c2;
         w_st += clock64() - c3;
       }
     }
-    if (a.probe && warp == 2 && lane == 0) {
+    if (ATX_PROBING && warp == 2 && lane == 0) {
       const long cta = (static_cast<long>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
       a.probe[cta * 12 + 2] = clock64() - t_sm0;
       a.probe[cta * 12 + 3] = w_s;
@@ -428,8 +434,11 @@ int launch_attention_bf16(const bf16* qkv, int B, int T, int NH, int Tc, bf16* o
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel,
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_tcgen05_kernel<true>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES);
     if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(attention)");
     attr_done[dev] = true;
   }
@@ -451,7 +460,10 @@ int launch_attention_bf16(const bf16* qkv, int B, int T, int NH, int Tc, bf16* o
     if (cudaMalloc(&a.probe, sizeof(long long) * 12 * nctas) != cudaSuccess) a.probe = nullptr;
     if (a.probe) cudaMemset(a.probe, 0, sizeof(long long) * 12 * nctas);
   }
-  attention_tcgen05_kernel<<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(tm, a);
+  if (a.probe)
+    attention_tcgen05_kernel<true><<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(tm, a);
+  else
+    attention_tcgen05_kernel<false><<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(tm, a);
   const int lrc = after_launch("attention_tcgen05_kernel");
   if (a.probe) {
     std::vector<long long> hbuf(12 * nctas);

@@ -48,7 +48,9 @@ constexpr int P_TMEM_COLS = 512;     // two accumulators of 256 columns
 constexpr int P_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 256 + 1024;
 
-template <int EPI, bool OUT_F32>
+// PROBE: cycle counters compiled in (diagnostic instantiation only; even behind a
+// runtime flag they slow the issue loops down).
+template <int EPI, bool OUT_F32, bool PROBE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                          const __grid_constant__ CUtensorMap tmW, const GemmArgs g,
@@ -109,14 +111,14 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       const int m0 = (tile / g.tiles_n) * (2 * P_BM) + static_cast<int>(rank) * P_BM;
       const int n0 = (tile % g.tiles_n) * P_BN + static_cast<int>(rank) * P_BN_HALF;
       for (int kb = 0; kb < KB; ++kb) {
-        const long long c0 = probe ? clock64() : 0;
+        const long long c0 = (PROBE && probe) ? clock64() : 0;
         if (!mbar_wait(&empty_bar[stage], phase ^ 1, wc, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
-        if (probe) w_empty += clock64() - c0;
+        if (PROBE && probe) w_empty += clock64() - c0;
         {
           uint8_t* sa = smem + stage * P_STAGE_BYTES;
           // all bytes of the stage (both CTAs) are credited to the leader's barrier
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
-          if (skip_loads && (tile != pair || kb >= P_STAGES)) {
+          if (PROBE && skip_loads && (tile != pair || kb >= P_STAGES)) {
             if (rank == 0) mbar_arrive(&full_bar[stage]);  // experiment: reuse stale operands
           } else {
             if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * P_STAGE_BYTES);
@@ -127,7 +129,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
       }
     }
-    if (probe) probe[blockIdx.x * 8 + 0] = w_empty;
+    if (PROBE && probe) probe[blockIdx.x * 8 + 0] = w_empty;
   } else if (warp == 1 && lane == 0) {
     // ------------------------------ MMA issuer (leader only) ------------------
     if (rank == 0) {
@@ -138,11 +140,11 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       bool ok = true;
       long long w_full = 0, w_tempty = 0;
       bool stage_ready = false;
-      const long long t_begin = probe ? clock64() : 0;
+      const long long t_begin = (PROBE && probe) ? clock64() : 0;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        const long long c0 = probe ? clock64() : 0;
+        const long long c0 = (PROBE && probe) ? clock64() : 0;
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, wc, DEV_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
-        if (probe) w_tempty += clock64() - c0;
+        if (PROBE && probe) w_tempty += clock64() - c0;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * P_BN);
         for (int kb = 0; kb < KB; ++kb) {
@@ -150,9 +152,9 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           // MMAs were being issued; only fall back to a blocking wait if that
           // early test failed.
           if (!stage_ready) {
-            const long long c1 = probe ? clock64() : 0;
+            const long long c1 = (PROBE && probe) ? clock64() : 0;
             if (!mbar_wait(&full_bar[stage], phase, wc, DEV_TIMEOUT_FULL)) { ok = false; break; }
-            if (probe) w_full += clock64() - c1;
+            if (PROBE && probe) w_full += clock64() - c1;
           }
           int ns = stage + 1;
           uint32_t np = phase;
@@ -178,7 +180,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
-      if (probe) {
+      if (PROBE && probe) {
         probe[blockIdx.x * 8 + 1] = w_full;
         probe[blockIdx.x * 8 + 2] = w_tempty;
         probe[blockIdx.x * 8 + 3] = clock64() - t_begin;
@@ -197,18 +199,18 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       const int n0 = (tile % g.tiles_n) * P_BN;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                              static_cast<uint32_t>(acc * P_BN);
-      const long long c0 = probe ? clock64() : 0;
+      const long long c0 = (PROBE && probe) ? clock64() : 0;
       if (!drain_tile<P_BN, EPI, OUT_F32>(t_row, m0 + row, n0, half, g, &tfull_bar[acc], acc_phase, wc,
-                                          probe ? w_epi : nullptr))
+                                          (PROBE && probe) ? w_epi : nullptr))
         break;
-      if (probe) t_epi += clock64() - c0;  // includes the wait for the accumulator
+      if (PROBE && probe) t_epi += clock64() - c0;  // includes the wait for the accumulator
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
-    if (probe && warp == 2 && lane == 0) {
+    if (PROBE && probe && warp == 2 && lane == 0) {
       probe[blockIdx.x * 8 + 4] = t_epi;
       probe[blockIdx.x * 8 + 5] = w_epi[0];
       probe[blockIdx.x * 8 + 6] = w_epi[1];
@@ -230,12 +232,15 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 template <int EPI, bool OUT_F32>
 int launch_pair_inst(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmArgs& g,
                      cudaStream_t stream) {
-  auto kern = gemm_pair_tcgen05_kernel<EPI, OUT_F32>;
+  auto kern = gemm_pair_tcgen05_kernel<EPI, OUT_F32, false>;
+  auto kern_probe = gemm_pair_tcgen05_kernel<EPI, OUT_F32, true>;
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(kern_probe, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
     if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(gemm_pair)");
     attr_done[dev] = true;
   }
@@ -257,7 +262,10 @@ int launch_pair_inst(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmA
     if (cudaMalloc(&probe, sizeof(long long) * 8 * 2 * pairs) != cudaSuccess) probe = nullptr;
     if (probe) cudaMemset(probe, 0, sizeof(long long) * 8 * 2 * pairs);
   }
-  kern<<<2 * pairs, P_THREADS, P_SMEM_BYTES, stream>>>(tmA, tmW, g, probe, skip_loads);
+  if (probe)
+    kern_probe<<<2 * pairs, P_THREADS, P_SMEM_BYTES, stream>>>(tmA, tmW, g, probe, skip_loads);
+  else
+    kern<<<2 * pairs, P_THREADS, P_SMEM_BYTES, stream>>>(tmA, tmW, g, nullptr, 0);
   const int rc = after_launch("gemm_pair_tcgen05_kernel");
   if (probe) {
     std::vector<long long> h(8 * 2 * pairs);
