@@ -59,3 +59,24 @@ def test_sampling_loop_matches_oracle(sd3, mode):
     else:
         rel = ((out.cpu() - ref).norm() / ref.norm()).item()
         assert rel < 2e-2  # guidance amplifies the per-call bf16 error (~3e-3) by (2g - 1)
+
+
+@pytest.mark.gpu
+def test_sampling_loop_as_one_cuda_graph_gives_the_same_bits(sd3):
+    g = golden("model_toy.pt")
+    cfg = g["config"]
+    m = sd3.Model(cfg["num_layers"], cfg["dual_attention_layers"], cfg["pooled_dim"], cfg["captions_dim"],
+                  cfg["in_channels"], cfg["emb_dim"], cfg["attn_heads"], cfg["mlp_expand"],
+                  cfg["patch_size"], cfg["pos_embed_max_size"], cfg["base_height"], True, sd3.PRECISION_BF16)
+    m.load({k: v.bfloat16().cuda() for k, v in g["params"].items()})
+    gen = torch.Generator().manual_seed(5)
+    un_caps = torch.randn(g["captions"].shape, generator=gen).bfloat16().cuda()
+    un_pool = torch.randn(g["pooled"].shape, generator=gen).bfloat16().cuda()
+    args = (g["latent"].bfloat16().cuda(), g["captions"].bfloat16().cuda(), g["pooled"].bfloat16().cuda(),
+            un_caps, un_pool)
+    eager = sd3.sample(m, *args, steps=3, guidance=4.5, shift=3.0)
+    graphed = sd3.sample(m, *args, steps=3, guidance=4.5, shift=3.0, use_graph=True)
+    torch.cuda.synchronize()
+    assert sd3.device_status() == 0
+    assert torch.equal(eager, graphed)
+    m.close()
