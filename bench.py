@@ -449,22 +449,25 @@ def main():
     h_t = tsteps.cpu().pin_memory()
     h_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
 
+    # The public serving call: HostPipeline.submit uploads the batch on a copy
+    # stream, runs the denoiser, downloads the result; with two device input sets
+    # the copies of neighbouring steps overlap the compute.  All of it is inside
+    # the timed region (the final download is waited for before e1).
+    pipe = s.HostPipeline(model, B, TC, 16, HW, HW, 2048, 4096, torch.bfloat16, depth=2)
+
     def e2e_step():
-        latent.copy_(h_lat, non_blocking=True)
-        captions.copy_(h_cap, non_blocking=True)
-        pooled.copy_(h_pool, non_blocking=True)
-        tsteps.copy_(h_t, non_blocking=True)
-        model.forward(pooled, captions, latent, tsteps, out)
-        h_out.copy_(out, non_blocking=True)
+        pipe.submit(h_pool, h_cap, h_lat, h_t, h_out)
 
     for _ in range(2):
         e2e_step()
+    pipe.flush()
     torch.cuda.synchronize()
     if dist:
         dist.barrier()
     e0.record()
     for _ in range(args.steps):
         e2e_step()
+    pipe.flush()
     e1.record()
     torch.cuda.synchronize()
     ms2 = e0.elapsed_time(e1)

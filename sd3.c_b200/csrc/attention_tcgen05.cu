@@ -60,6 +60,22 @@ struct AttnArgs {
   long long* probe;  // diagnostics (SD3_ATTN_PROBE=1): 8 counters per CTA, else null
 };
 
+// O *= alpha for this thread's query row (64 fp32 columns in TMEM).  Rare (the
+// running maximum has to move by more than 2^8), so it is kept out of line: its
+// 16 extra live registers and its code would otherwise weigh on the hot loop.
+__device__ __noinline__ void rescale_o(uint32_t o_tmem, float alpha) {
+  tc_fence_after_sync();
+  uint32_t o0[16];
+#pragma unroll 1
+  for (int part = 0; part < 4; ++part) {
+    tmem_ld_32x32b_x16(o_tmem + 16 * part, o0);
+    tmem_wait_ld();
+#pragma unroll
+    for (int i = 0; i < 16; ++i) o0[i] = __float_as_uint(__uint_as_float(o0[i]) * alpha);
+    tmem_st_32x32b_x16(o_tmem + 16 * part, o0);
+  }
+}
+
 // Cycle counters are compiled in only in the PROBE instantiation: even behind a
 // runtime flag they cost the softmax loop about a tenth of its throughput.
 #define ATX_PROBING (PROBE && a.probe != nullptr)
@@ -294,18 +310,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
           // P_{t-1} V_{t-1} must have landed in O before O is rescaled; the
           // product of this sub-tile is only issued after p_ready below.
           if (!mbar_wait_warp(&pv_done[(t - 1) & 1], ((t - 1) >> 1) & 1, wc, DEV_TIMEOUT_ATTN_O)) { ok = false; break; }
-          tc_fence_after_sync();
-          uint32_t o0[32];
-          tmem_ld_32x32b_x32(o_tmem, o0);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o0[i] = __float_as_uint(__uint_as_float(o0[i]) * alpha);
-          tmem_st_32x32b_x32(o_tmem, o0);
-          tmem_ld_32x32b_x32(o_tmem + 32, o0);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o0[i] = __float_as_uint(__uint_as_float(o0[i]) * alpha);
-          tmem_st_32x32b_x32(o_tmem + 32, o0);
+          rescale_o(o_tmem, alpha);
         }
       }
       const float mc = m_used * c;

@@ -377,6 +377,63 @@ class Model:
         return c, x
 
 
+class HostPipeline:
+    """Runs the denoiser on batches that live in pinned host memory.
+
+    Every `submit` uploads one batch, runs `model.forward` on it and downloads the
+    result into the caller's host buffer.  Uploads go through a copy stream of
+    their own into one of `depth` device input sets, downloads through a second
+    one, so the upload of batch i+1 and the download of batch i-1 overlap the
+    compute of batch i; the order of work on a set is kept by events.  Nothing
+    is allocated after construction.  `flush()` makes the current stream wait
+    for the last download (call it before reading the host buffers or timing)."""
+
+    def __init__(self, model, B, Tc, C, H, W, pooled_dim, captions_dim, dtype=None, depth=2):
+        torch = _torch()
+        dtype = dtype or torch.bfloat16
+        self.model = model
+        self.h2d = torch.cuda.Stream()
+        self.d2h = torch.cuda.Stream()
+        self.sets = []
+        for _ in range(max(1, depth)):
+            self.sets.append(dict(
+                latent=torch.empty(B, C, H, W, device="cuda", dtype=dtype),
+                captions=torch.empty(B, Tc, captions_dim, device="cuda", dtype=dtype),
+                pooled=torch.empty(B, pooled_dim, device="cuda", dtype=dtype),
+                t=torch.empty(B, device="cuda", dtype=torch.float32),
+                out=torch.empty(B, C, H, W, device="cuda", dtype=dtype),
+                uploaded=torch.cuda.Event(), computed=torch.cuda.Event(), drained=torch.cuda.Event()))
+        self.count = 0
+        self.last = None
+        model.reserve(B, Tc, H, W)
+
+    def submit(self, h_pooled, h_captions, h_latent, h_timesteps, h_out):
+        torch = _torch()
+        st = self.sets[self.count % len(self.sets)]
+        self.count += 1
+        cur = torch.cuda.current_stream()
+        with torch.cuda.stream(self.h2d):
+            self.h2d.wait_event(st["computed"])  # the compute that last read this set is over
+            st["latent"].copy_(h_latent, non_blocking=True)
+            st["captions"].copy_(h_captions, non_blocking=True)
+            st["pooled"].copy_(h_pooled, non_blocking=True)
+            st["t"].copy_(h_timesteps, non_blocking=True)
+            st["uploaded"].record(self.h2d)
+        cur.wait_event(st["uploaded"])
+        cur.wait_event(st["drained"])  # the download that last read this set's output is over
+        self.model.forward(st["pooled"], st["captions"], st["latent"], st["t"], st["out"])
+        st["computed"].record(cur)
+        with torch.cuda.stream(self.d2h):
+            self.d2h.wait_event(st["computed"])
+            h_out.copy_(st["out"], non_blocking=True)
+            st["drained"].record(self.d2h)
+        self.last = st
+
+    def flush(self):
+        if self.last is not None:
+            _torch().cuda.current_stream().wait_event(self.last["drained"])
+
+
 def shard_range(n, world, rank):
     """Contiguous slice [lo, hi) of n independent samples owned by `rank` of
     `world` ranks (sizes differ by at most one).  Samples never interact in the
