@@ -39,6 +39,10 @@ STEP_TFLOP = 89.997
 B, TC, HW, TX = 8, 333, 128, 4096
 E, NH, FH = 1536, 24, 6144
 T = TC + TX
+# DRAM bytes (read + written) of one joint-attention launch per sample, from the ncu
+# capture of `--profile-case attn_joint` (batch 2: 81.68 MB read + 8.00 MB written);
+# it is the compulsory q|k|v read and O write, so it grows in proportion to the batch.
+ATTN_TRAFFIC_BYTES_PER_SAMPLE = int((81.68e6 + 8.00e6) / 2)
 
 
 def load_binding():
@@ -496,7 +500,9 @@ def main():
     if joint is not None:
         roofline = {"bound": "tensor", "kernel": "attention_tcgen05_kernel (joint, T=4429, B=8, 24 heads)",
                     "achieved": joint["achieved"], "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                    "frac": joint["frac"], "traffic": None, "peak_source": peaks["source"] + " burst"}
+                    "frac": joint["frac"], "traffic": ATTN_TRAFFIC_BYTES_PER_SAMPLE * B,
+                    "traffic_source": "ncu dram__bytes_read+write of the batch-2 capture in profiles/, per sample x batch",
+                    "peak_source": peaks["source"] + " burst"}
     else:
         roofline = {"bound": "tensor", "kernel": "whole step", "achieved": round(step_tf, 1),
                     "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
