@@ -175,3 +175,57 @@ def test_config2_full_model_bf16(sd3):
     r = rel_l2(out, ref)
     print("config2 rel_l2", r)
     assert r < 1e-2
+
+
+def _block_case(sd3, B, Tx, Tc, seed, dual):
+    """One MMDiT-X block at SD3.5-medium width in bf16 against the oracle run in
+    fp32 on the GPU (TF32 off) on the same bf16-rounded weights and inputs."""
+    E, NH = 1536, 24
+    shapes = O.block_param_shapes(E, 4, 64, dual, False, True)
+    p = O.random_params(shapes, seed=seed, std=0.02, dtype=torch.bfloat16, norm_std=0.1)
+    gen = torch.Generator().manual_seed(seed)
+    x = torch.randn(B, Tx, E, generator=gen).bfloat16().float()
+    c = torch.randn(B, Tc, E, generator=gen).bfloat16().float()
+    y = torch.nn.functional.silu(torch.randn(B, E, generator=gen))
+    m = sd3.Model(1, [0] if dual else [], 0, 0, 0, E, NH, 4, 0, 0, 0, True, sd3.PRECISION_BF16,
+                  last_discards_context=False, block_only=True)
+    m.load({k: v.cuda() for k, v in p.items()}, prefix="transformer.0.")
+    cc, xx = c.cuda().clone(), x.cuda().clone()
+    m.block_forward(0, y.cuda(), cc, xx)
+    torch.cuda.synchronize()
+    assert sd3.device_status() == 0
+    tf32 = (torch.backends.cuda.matmul.allow_tf32, torch.backends.cudnn.allow_tf32)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    try:
+        with torch.no_grad():
+            pf = {k: v.float().cuda() for k, v in p.items()}
+            c_ref, x_ref = O.dit_block(x.cuda(), c.cuda(), y.cuda(), pf, NH, dual, True, False)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32, torch.backends.cudnn.allow_tf32 = tf32
+    return m, (x, c, y), (xx, cc), (x_ref, c_ref)
+
+
+def test_config3_block_full_size_and_batch_independence(sd3):
+    """BASELINE config 3 shapes (batch 8, 4096 image + 333 context tokens), one
+    dual block: parity with the oracle, and the size-independent property the
+    path offers: samples never interact, so sample b of the batch-8 call has
+    the same bits as a batch-1 call on that sample."""
+    m, (x, c, y), (xx, cc), (x_ref, c_ref) = _block_case(sd3, 8, 4096, 333, seed=2, dual=True)
+    assert rel_l2(xx, x_ref.cpu()) < 1e-2
+    assert rel_l2(cc, c_ref.cpu()) < 1e-2
+    for b in (0, 5):
+        c1, x1 = c[b:b + 1].cuda().clone(), x[b:b + 1].cuda().clone()
+        m.block_forward(0, y[b:b + 1].cuda(), c1, x1)
+        torch.cuda.synchronize()
+        assert torch.equal(x1[0], xx[b]) and torch.equal(c1[0], cc[b])
+    m.close()
+
+
+def test_config5_block_long_sequence(sd3):
+    """BASELINE config 5 shapes: one 2048x2048 image, 16384 image + 333 context
+    tokens (131 key tiles per attention row), one plain block, batch 1."""
+    m, _, (xx, cc), (x_ref, c_ref) = _block_case(sd3, 1, 16384, 333, seed=4, dual=False)
+    assert rel_l2(xx, x_ref.cpu()) < 1e-2
+    assert rel_l2(cc, c_ref.cpu()) < 1e-2
+    m.close()
