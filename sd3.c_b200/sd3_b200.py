@@ -16,7 +16,7 @@ import os
 from ctypes import c_char_p, c_float, c_int, c_int64, c_long, c_uint64, c_void_p, POINTER
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libsd3_b200.so")
+LIB_PATH = os.environ.get("SD3_B200_LIB") or os.path.join(HERE, "libsd3_b200.so")
 
 DTYPE_F32 = 0
 DTYPE_BF16 = 1
