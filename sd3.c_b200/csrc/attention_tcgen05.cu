@@ -6,14 +6,20 @@
 // One CTA owns a 128-query tile of one (sample, head); two CTAs are resident
 // per SM.  Warp 0 streams K and V tiles (128 keys per stage) with TMA from the
 // packed (B, T, 3E) q|k|v buffer.  The keys are consumed in sub-tiles of 64:
-// warp 1 issues S_t = Q K_t^T into one of two 64-column TMEM buffers, always
-// one sub-tile ahead of the softmax, so the four softmax warps (one query row
-// per thread, TMEM lane == row) find their scores ready and never wait for the
-// tensor pipe.  They turn S_t into P_t = exp2(S c - m c) in place (bf16, two
-// per TMEM column, over the first 32 columns of the same buffer), and warp 1
-// then issues O += P_t V_t with P read from TMEM and V from shared memory in
-// MN-major form, followed by S_{t+2} into the buffer just freed.  The T x T
+// warp 1 issues S_t = Q K_t^T into one of three 64-column TMEM buffers, two
+// sub-tiles ahead of the softmax, so the four softmax warps (one query row per
+// thread, TMEM lane == row) normally find their scores ready.  They turn S_t
+// into P_t = exp2(S c - m c) in place (bf16, two per TMEM column, over the
+// first 32 columns of the same buffer), and warp 1 then issues O += P_t V_t
+// with P read from TMEM and V from shared memory in MN-major form.  The T x T
 // score matrix never exists in memory.
+//
+// Two independent CTAs per SM matter: the exponentials are the scarce resource
+// at head_dim 64 (one MUFU op per 256 tensor FLOP), each softmax warp runs a
+// serial chain (scores ready, TMEM load, row max, exponentials, store,
+// hand-off), and two CTAs that drift apart fill each other's gaps.  Variants
+// with one larger CTA per SM (two query tiles sharing K/V, 128-key score
+// tiles) were measured slower because their two pipelines fall into lockstep.
 //
 // Replaces mha_cuda (cuda/dit.cu:612-652: two cublasSgemmStridedBatched calls
 // around scale_softmax_kernel2, cuda/dit.cu:548-608, over materialised T x T

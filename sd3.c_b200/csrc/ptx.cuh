@@ -123,22 +123,11 @@ struct WaitCtx {
 // CTA already aborted; the caller must then stop issuing work.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w,
                                           int code) {
-#ifdef SD3_WAIT_SPINS
-  // test_wait never suspends the thread: a role with nothing else to do sees the
-  // phase flip a few cycles after it happens instead of after a wake-up.
-  if (mbar_test_wait(bar, parity)) return true;
-#else
   if (mbar_try_wait(bar, parity)) return true;
-#endif
   const uint64_t t0 = global_timer_ns();
   uint32_t it = 0;
   while (true) {
-#ifdef SD3_WAIT_SPINS
-    if (mbar_test_wait(bar, parity)) return true;
-    __nanosleep(SD3_WAIT_SPINS);
-#else
     if (mbar_try_wait(bar, parity)) return true;
-#endif
     if (((++it) & 0xffu) == 0) {
       if (*w.s_abort) return false;
       if (global_timer_ns() - t0 > SD3_WAIT_LIMIT_NS) {
@@ -148,11 +137,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
       }
     }
   }
-}
-
-// Named barrier over `count` threads (a multiple of 32); id 0 is __syncthreads'.
-__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t count) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
 // Warp-wide bounded wait: lane 0 polls, the other lanes park at the shuffle, so
