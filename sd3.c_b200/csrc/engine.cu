@@ -57,6 +57,7 @@ struct Workspace {
   float *temb, *th, *tout, *ph, *y, *mod, *c, *x, *pooled_f32;
   // activation-dtype buffers (bf16, or f32 in the exact mode)
   void *cap_in, *patches, *h_c, *h_x, *h_x2, *qkv, *qkv2, *o_c, *o_x, *o_x2, *hid_x, *hid_c;
+  bf16* y_bf = nullptr;  // conditioning vector as a GEMM operand
   // position table cache
   float* pos = nullptr;
   int pos_h = 0, pos_w = 0;
@@ -236,7 +237,7 @@ int reserve_ws(sd3_model* m, int B, int Tc, int Tx) {
   struct Item { void** p; size_t bytes; };
   std::vector<Item> items = {
       {(void**)&w.temb, nB * 256 * 4}, {(void**)&w.th, nB * E * 4}, {(void**)&w.tout, nB * E * 4},
-      {(void**)&w.ph, nB * E * 4}, {(void**)&w.y, nB * E * 4},
+      {(void**)&w.ph, nB * E * 4}, {(void**)&w.y, nB * E * 4}, {(void**)&w.y_bf, nB * E * 2},
       {(void**)&w.mod, nB * static_cast<size_t>(m->ada_total) * 4},
       {(void**)&w.c, nTc * E * 4}, {(void**)&w.x, nTx * E * 4},
       {(void**)&w.pooled_f32, nB * static_cast<size_t>(c.pooled_dim > 0 ? c.pooled_dim : 1) * 4},
@@ -648,8 +649,24 @@ int sd3_dit_forward(sd3_model* m, const void* pooled, const void* captions, cons
   SD3_TRY(launch_skinny_linear(pooled32, c.pooled_dim, m->p1.w, m->f32, m->p1.b, nullptr, 0, w.ph, E, B, E, c.pooled_dim, 1, st));
   SD3_TRY(launch_skinny_linear(w.ph, E, m->p2.w, m->f32, m->p2.b, w.tout, E, w.y, E, B, E, E, 1, st));
   // every AdaLN vector of every block and of the final layer in one launch
-  SD3_TRY(launch_skinny_linear(w.y, E, m->ada_w, m->f32, m->ada_b, nullptr, 0, w.mod, m->ada_total, B,
-                               static_cast<int>(m->ada_total), E, 0, st));
+  if (!m->f32 && m->ada_total % 64 == 0 && E % 64 == 0) {
+    // As a tensor-core GEMM with M = batch: out (B, ada_total) = y W^T + b.  Only B
+    // of the 128 rows of each MMA carry data, but the tensor pipe has the room
+    // and TMA streams the 1.5 GB of weights at HBM speed, which the SIMT kernel
+    // (8 warps per SM at its register count) does not.
+    SD3_TRY(launch_cast_f32_to_bf16(w.y, w.y_bf, static_cast<long>(B) * E, st));
+    GemmEpilogue e;
+    e.mode = EPI_BIAS;
+    e.bias = m->ada_b;
+    e.out = w.mod;
+    e.out_f32 = 1;
+    e.ldo = m->ada_total;
+    SD3_TRY(launch_gemm(w.y_bf, E, m->ada_w, E, OPERAND_BF16, B, static_cast<int>(m->ada_total), E, e,
+                        m->status, st));
+  } else {
+    SD3_TRY(launch_skinny_linear(w.y, E, m->ada_w, m->f32, m->ada_b, nullptr, 0, w.mod, m->ada_total, B,
+                                 static_cast<int>(m->ada_total), E, 0, st));
+  }
   // context stream c = captions W + b
   {
     const void* cap_in = captions;
