@@ -73,6 +73,20 @@ SD3_API int sd3_device_status(int* status_out);
 SD3_API int sd3_linear(const void* x_bf16, const void* w_nk_bf16, const float* bias, void* out,
                int out_dtype, int M, int N, int K, int act, void* stream);
 
+/* The same contraction on e4m3 operands (tcgen05 kind::f8f6f4, fp32
+ * accumulation): out = act(scale * sum_k x[m,k] w[n,k] + bias[n]), x (M,K) and
+ * w (N,K) one byte per element, scale = the product of the two operands'
+ * quantisation scales.  K must be a multiple of 16.  The reference has no
+ * reduced-precision path; this is the FP8 variant of launch_linear
+ * (cuda/dit.cu:683-756). */
+SD3_API int sd3_linear_e4m3(const void* x_e4m3, const void* w_nk_e4m3, const float* bias, void* out,
+                    int out_dtype, int M, int N, int K, float scale, int act, void* stream);
+
+/* out[i] = e4m3(saturate(in[i] / scale)), round to nearest even; in f32 or bf16
+ * (in_dtype), n a multiple of 4.  Producer of sd3_linear_e4m3 operands. */
+SD3_API int sd3_quantize_e4m3(const void* in, int in_dtype, void* out_e4m3, long n, float scale,
+                      void* stream);
+
 /* Same contraction in exact fp32 arithmetic (SIMT); x, w, out are f32.
  * Replaces the CPU `linear` (modules.cpp:475-490) for fp32 tensors. */
 SD3_API int sd3_linear_f32(const float* x, const float* w_nk, const float* bias, float* out, int M, int N,

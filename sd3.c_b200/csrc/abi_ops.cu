@@ -77,6 +77,30 @@ int sd3_linear(const void* x, const void* w, const float* bias, void* out, int o
   return launch_gemm(x, K, w, K, OPERAND_BF16, M, N, K, e, device_status_word(), S(stream));
 }
 
+int sd3_linear_e4m3(const void* x, const void* w, const float* bias, void* out, int out_dtype, int M,
+                    int N, int K, float scale, int act, void* stream) {
+  if (!dtype_ok(out_dtype) || (act != SD3_ACT_NONE && act != SD3_ACT_GELU_TANH)) {
+    set_last_error("sd3_linear_e4m3: bad out_dtype %d or act %d", out_dtype, act);
+    return SD3_ERR_INVALID_ARG;
+  }
+  GemmEpilogue e;
+  e.mode = act == SD3_ACT_GELU_TANH ? EPI_BIAS_GELU : EPI_BIAS;
+  e.bias = bias;
+  e.out = out;
+  e.out_f32 = out_dtype == SD3_DTYPE_F32;
+  e.ldo = N;
+  e.alpha = scale;
+  return launch_gemm(x, K, w, K, OPERAND_E4M3, M, N, K, e, device_status_word(), S(stream));
+}
+
+int sd3_quantize_e4m3(const void* in, int in_dtype, void* out, long n, float scale, void* stream) {
+  if (!dtype_ok(in_dtype) || !(scale > 0.f)) {
+    set_last_error("sd3_quantize_e4m3: bad dtype %d or scale %g", in_dtype, static_cast<double>(scale));
+    return SD3_ERR_INVALID_ARG;
+  }
+  return launch_quantize_e4m3(in, in_dtype == SD3_DTYPE_F32, out, n, 1.0f / scale, S(stream));
+}
+
 int sd3_linear_f32(const float* x, const float* w, const float* bias, float* out, int M, int N,
                    int K, int act, void* stream) {
   if (act != SD3_ACT_NONE && act != SD3_ACT_GELU_TANH) {

@@ -121,6 +121,11 @@ int launch_patchify(const void* latent, int in_f32, void* out, int out_f32, int 
 
 // element-wise casts / transposes used by weight packing and the per-op API
 int launch_cast_f32_to_bf16(const float* in, bf16* out, long n, cudaStream_t stream);
+// e4m3 operand = saturate(in * inv_scale) (round to nearest even); n % 4 == 0.
+int launch_quantize_e4m3(const void* in, int in_f32, void* out, long n, float inv_scale,
+                         cudaStream_t stream);
+// *out = max |in[i]| (fp32, device memory)
+int launch_absmax(const void* in, int in_f32, long n, float* out, cudaStream_t stream);
 int launch_cast_bf16_to_f32(const bf16* in, float* out, long n, cudaStream_t stream);
 // in: (R, C) row-major of in dtype -> out: (C, R) row-major of out dtype
 int launch_transpose(const void* in, int in_f32, void* out, int out_f32, int R, int C,

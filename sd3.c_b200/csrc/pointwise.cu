@@ -441,6 +441,94 @@ int launch_patchify(const void* latent, int in_f32, void* out, int out_f32, int 
   return after_launch("patchify_kernel");
 }
 
+// ----------------------------------------------------------------------------
+// e4m3 operands for the FP8 GEMM: out = saturate(in * inv_scale), round to
+// nearest even; and the absolute maximum a scale is derived from.
+// ----------------------------------------------------------------------------
+namespace {
+
+__device__ __forceinline__ uint16_t pack_e4m3x2(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+template <typename TI>
+__global__ void quantize_e4m3_kernel(const TI* __restrict__ in, uint8_t* __restrict__ out, long n,
+                                     float inv_scale) {
+  // four elements per thread per step (n is a multiple of 4)
+  long i = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x * 4;
+  for (; i < n; i += stride) {
+    float v[4];
+    if constexpr (sizeof(TI) == 4) {
+      const float4 f = *reinterpret_cast<const float4*>(in + i);
+      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    } else {
+      const uint2 u = *reinterpret_cast<const uint2*>(in + i);
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+      v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    }
+    const uint32_t lo = pack_e4m3x2(v[0] * inv_scale, v[1] * inv_scale);
+    const uint32_t hi = pack_e4m3x2(v[2] * inv_scale, v[3] * inv_scale);
+    *reinterpret_cast<uint32_t*>(out + i) = lo | (hi << 16);
+  }
+}
+
+template <typename TI>
+__global__ void absmax_kernel(const TI* __restrict__ in, long n, unsigned* __restrict__ out_bits) {
+  float m = 0.f;
+  long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  for (; i < n; i += stride) {
+    float v;
+    if constexpr (sizeof(TI) == 4) v = in[i]; else v = __bfloat162float(in[i]);
+    m = fmaxf(m, fabsf(v));
+  }
+  m = warp_max(m);
+  // non-negative floats order like their bit patterns
+  if ((threadIdx.x & 31) == 0) atomicMax(out_bits, __float_as_uint(m));
+}
+
+}  // namespace
+
+int launch_quantize_e4m3(const void* in, int in_f32, void* out, long n, float inv_scale,
+                         cudaStream_t stream) {
+  if (!in || !out || n <= 0 || n % 4 != 0 || (reinterpret_cast<uintptr_t>(in) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 3)) {
+    set_last_error("quantize_e4m3: need n %% 4 == 0 and aligned pointers (n %ld)", n);
+    return ST_INVALID_ARG;
+  }
+  const long blocks = (n / 4 + 255) / 256;
+  const unsigned grid = static_cast<unsigned>(blocks < 148 * 16 ? blocks : 148 * 16);
+  if (in_f32)
+    quantize_e4m3_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(in),
+                                                          static_cast<uint8_t*>(out), n, inv_scale);
+  else
+    quantize_e4m3_kernel<bf16><<<grid, 256, 0, stream>>>(static_cast<const bf16*>(in),
+                                                         static_cast<uint8_t*>(out), n, inv_scale);
+  return after_launch("quantize_e4m3_kernel");
+}
+
+int launch_absmax(const void* in, int in_f32, long n, float* out, cudaStream_t stream) {
+  if (!in || !out || n <= 0) {
+    set_last_error("absmax: invalid argument");
+    return ST_INVALID_ARG;
+  }
+  cudaError_t e = cudaMemsetAsync(out, 0, 4, stream);
+  if (e != cudaSuccess) return check_cuda(e, "cudaMemsetAsync(absmax)");
+  const long blocks = (n + 255) / 256;
+  const unsigned grid = static_cast<unsigned>(blocks < 148 * 8 ? blocks : 148 * 8);
+  if (in_f32)
+    absmax_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(in), n,
+                                                   reinterpret_cast<unsigned*>(out));
+  else
+    absmax_kernel<bf16><<<grid, 256, 0, stream>>>(static_cast<const bf16*>(in), n,
+                                                  reinterpret_cast<unsigned*>(out));
+  return after_launch("absmax_kernel");
+}
+
 int launch_cast_f32_to_bf16(const float* in, bf16* out, long n, cudaStream_t stream) {
   if (n <= 0) return ST_OK;
   const unsigned grid = static_cast<unsigned>(n / 256 + 1 < 148 * 16 ? n / 256 + 1 : 148 * 16);

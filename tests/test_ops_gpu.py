@@ -205,3 +205,36 @@ def test_rmsnorm_heads(sd3):
     ref[:, 3:6] = ref[:, 3:6] * torch.rsqrt(ref[:, 3:6].pow(2).mean(-1, keepdim=True) + 1e-6) * w
     sd3.rmsnorm_heads(x, 96, 3, 32, w, 1e-6)
     assert (x.view(10, 9, 32) - ref).abs().max().item() < 1e-5
+
+
+@pytest.mark.parametrize("M,N,K,act", [(512, 768, 1536, 0), (333, 1536, 6144, 1), (129, 192, 1552, 0),
+                                       (4096, 4608, 1536, 0), (64, 64, 128, 0)])
+def test_linear_e4m3_matches_the_same_contraction_in_fp32(sd3, M, N, K, act):
+    """FP8 GEMM (tcgen05 kind::f8f6f4): quantise both operands with per-tensor
+    scales, then compare with the fp32 product of the very same e4m3 values, so
+    the only difference left is the accumulation order."""
+    gen = torch.Generator(device="cuda").manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=gen, device="cuda")
+    w = torch.randn(N, K, generator=gen, device="cuda") * 0.02
+    bias = torch.randn(N, generator=gen, device="cuda") * 0.1
+    sx = x.abs().max().item() / 448.0
+    sw = w.abs().max().item() / 448.0
+    x8 = torch.empty(M, K, device="cuda", dtype=torch.uint8)
+    w8 = torch.empty(N, K, device="cuda", dtype=torch.uint8)
+    sd3.check(sd3.lib().sd3_quantize_e4m3(sd3.ptr(x), sd3.DTYPE_F32, sd3.ptr(x8), M * K, sx, sd3.stream_ptr()))
+    sd3.check(sd3.lib().sd3_quantize_e4m3(sd3.ptr(w.bfloat16()), sd3.DTYPE_BF16, sd3.ptr(w8), N * K, sw,
+                                          sd3.stream_ptr()))
+    # the quantiser rounds to nearest even like torch's conversion
+    assert torch.equal(x8.view(torch.float8_e4m3fn).float(), (x / sx).to(torch.float8_e4m3fn).float())
+    assert torch.equal(w8.view(torch.float8_e4m3fn).float(),
+                       (w.bfloat16().float() / sw).to(torch.float8_e4m3fn).float())
+    out = torch.empty(M, N, device="cuda", dtype=torch.float32)
+    sd3.check(sd3.lib().sd3_linear_e4m3(sd3.ptr(x8), sd3.ptr(w8), sd3.ptr(bias), sd3.ptr(out), sd3.DTYPE_F32,
+                                        M, N, K, sx * sw, act, sd3.stream_ptr()))
+    torch.cuda.synchronize()
+    assert sd3.device_status() == 0
+    ref = (x8.view(torch.float8_e4m3fn).double() @ w8.view(torch.float8_e4m3fn).double().t()) * (sx * sw) + bias.double()
+    if act:
+        ref = torch.nn.functional.gelu(ref, approximate="tanh")
+    err = (out.double() - ref).abs().max().item()
+    assert err < 2e-3 * max(1.0, ref.abs().max().item()), err
