@@ -36,6 +36,9 @@ struct Linear {
   void* w = nullptr;   // packed (N, K), bf16 or f32 depending on the model precision
   float* b = nullptr;  // (N,) f32
   int N = 0, K = 0;
+  // FP8 mode: the same matrix as e4m3 = round(w / wscale), wscale = max|w| / 448
+  void* w8 = nullptr;
+  float wscale = 1.0f;
 };
 
 struct LayerW {
@@ -58,6 +61,7 @@ struct Workspace {
   // activation-dtype buffers (bf16, or f32 in the exact mode)
   void *cap_in, *patches, *h_c, *h_x, *h_x2, *qkv, *qkv2, *o_c, *o_x, *o_x2, *hid_x, *hid_c;
   bf16* y_bf = nullptr;  // conditioning vector as a GEMM operand
+  void* a8 = nullptr;    // FP8 mode: e4m3 copy of the current GEMM's left operand
   // position table cache
   float* pos = nullptr;
   int pos_h = 0, pos_w = 0;
@@ -73,6 +77,7 @@ struct sd3_model {
   sd3_config cfg;
   int E = 0, NH = 0, D = 0, F = 0, Kp = 0, Nout = 0;
   bool f32 = false;
+  bool fp8 = false;  // bf16 everywhere except the block GEMMs, which take e4m3 operands
   std::vector<LayerW> layers;
   Linear t1, t2, p1, p2, cap, patch, fin;
   void* ada_w = nullptr;  // (ada_total, E)
@@ -247,6 +252,7 @@ int reserve_ws(sd3_model* m, int B, int Tc, int Tx) {
       {&w.qkv, nB * T * 3 * E * ab}, {&w.qkv2, nTx * 3 * E * ab},
       {&w.o_c, nTc * E * ab}, {&w.o_x, nTx * E * ab}, {&w.o_x2, nTx * E * ab},
       {&w.hid_x, nTx * F * ab}, {&w.hid_c, nTc * F * ab},
+      {&w.a8, m->fp8 ? (nTx > nTc ? nTx : nTc) * F : 16},
   };
   size_t total = 0;
   for (auto& it : items) total += align_up(it.bytes, 256);
@@ -277,6 +283,15 @@ int run_linear(sd3_model* m, const Linear& L, const void* A, int M, const GemmEp
   if (m->f32)
     return launch_gemm_f32(static_cast<const float*>(A), L.K, static_cast<const float*>(L.w), L.K,
                            M, L.N, L.K, ee, st);
+  if (m->fp8 && L.w8) {
+    // e4m3 x e4m3: the bf16 operand is converted as is (scale 1: LayerNorm
+    // outputs, attention outputs and GELU outputs sit well inside e4m3's range and
+    // the conversion saturates), the weight's scale is undone in the epilogue.
+    int rc = launch_quantize_e4m3(A, 0, m->ws.a8, static_cast<long>(M) * L.K, 1.0f, st);
+    if (rc) return rc;
+    ee.alpha = L.wscale;
+    return launch_gemm(m->ws.a8, L.K, L.w8, L.K, OPERAND_E4M3, M, L.N, L.K, ee, m->status, st);
+  }
   return launch_gemm(A, L.K, L.w, L.K, OPERAND_BF16, M, L.N, L.K, ee, m->status, st);
 }
 
@@ -395,6 +410,36 @@ int block_body(sd3_model* m, int l, float* c, float* x, int B, int Tc, int Tx, c
   return ST_OK;
 }
 
+// FP8 mode: every block GEMM weight gets an e4m3 twin with one scale per matrix.
+int quantize_block_weights(sd3_model* m) {
+  float* d_amax = nullptr;
+  int rc = check_cuda(cudaDeviceSynchronize(), "parameter copies");  // whatever stream packed them
+  if (rc) return rc;
+  rc = dev_alloc(m, reinterpret_cast<void**>(&d_amax), 4);
+  if (rc) return rc;
+  for (LayerW& Lw : m->layers) {
+    Linear* all[] = {&Lw.c_qkv, &Lw.c_out, &Lw.c_mlp1, &Lw.c_mlp2, &Lw.x_qkv,
+                     &Lw.x_out, &Lw.x_mlp1, &Lw.x_mlp2, &Lw.d_qkv, &Lw.d_out};
+    for (Linear* L : all) {
+      if (!L->w || L->w8) continue;
+      const long n = static_cast<long>(L->N) * L->K;
+      if (n % 4 || L->K % 16) continue;  // stays bf16
+      rc = launch_absmax(L->w, 0, n, d_amax, nullptr);
+      if (rc) return rc;
+      float amax = 0.f;
+      rc = check_cuda(cudaMemcpy(&amax, d_amax, 4, cudaMemcpyDeviceToHost), "read absmax");
+      if (rc) return rc;
+      if (!(amax > 0.f)) amax = 1.0f;
+      L->wscale = amax / 448.0f;
+      rc = dev_alloc(m, &L->w8, static_cast<size_t>(n));
+      if (rc) return rc;
+      rc = launch_quantize_e4m3(L->w, 0, L->w8, n, 1.0f / L->wscale, nullptr);
+      if (rc) return rc;
+    }
+  }
+  return check_cuda(cudaDeviceSynchronize(), "quantize weights");
+}
+
 }  // namespace
 
 extern "C" {
@@ -407,7 +452,8 @@ int sd3_model_create(const sd3_config* cfg, sd3_model** out) {
                    cfg->num_layers, cfg->emb_dim, cfg->attn_heads);
     return SD3_ERR_INVALID_ARG;
   }
-  if (cfg->precision != SD3_PRECISION_BF16 && cfg->precision != SD3_PRECISION_F32) {
+  if (cfg->precision != SD3_PRECISION_BF16 && cfg->precision != SD3_PRECISION_F32 &&
+      cfg->precision != SD3_PRECISION_FP8) {
     set_last_error("sd3_model_create: precision %d not available", cfg->precision);
     return SD3_ERR_UNSUPPORTED;
   }
@@ -428,6 +474,7 @@ int sd3_model_create(const sd3_config* cfg, sd3_model** out) {
   m->Kp = cfg->block_only ? 0 : cfg->in_channels * cfg->patch_size * cfg->patch_size;
   m->Nout = m->Kp;
   m->f32 = cfg->precision == SD3_PRECISION_F32;
+  m->fp8 = cfg->precision == SD3_PRECISION_FP8;
   if (m->D > 128) {
     set_last_error("sd3_model_create: head_dim %d > 128 unsupported", m->D);
     delete m;
@@ -559,6 +606,10 @@ int sd3_model_finalize(sd3_model* m, int* missing) {
   if (n) {
     set_last_error("%d required parameter(s) missing, first: %s", n, first.c_str());
     return SD3_ERR_NOT_READY;
+  }
+  if (m->fp8 && !m->finalized) {
+    int rc = quantize_block_weights(m);
+    if (rc) return rc;
   }
   m->finalized = true;
   return SD3_OK;

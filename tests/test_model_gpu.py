@@ -175,6 +175,17 @@ def test_config2_full_model_bf16(sd3):
     r = rel_l2(out, ref)
     print("config2 rel_l2", r)
     assert r < 1e-2
+    # FP8 mode on the same weights and inputs: e4m3 block GEMMs (three mantissa bits per
+    # operand, one scale per weight matrix, no calibration); measured 5.0e-2, bar 8e-2
+    m8 = sd3.Model(24, range(13), 2048, 4096, 16, 1536, 24, 4, 2, 384, 128, True, sd3.PRECISION_FP8)
+    m8.load({k: v.cuda() for k, v in p.items()})
+    out8 = m8.forward(pooled.cuda(), captions.cuda(), latent.cuda(), t.cuda())
+    torch.cuda.synchronize()
+    assert sd3.device_status() == 0
+    m8.close()
+    r8 = rel_l2(out8, ref)
+    print("config2 fp8 rel_l2", r8)
+    assert r8 < 8e-2
 
 
 def _block_case(sd3, B, Tx, Tc, seed, dual):
@@ -228,4 +239,21 @@ def test_config5_block_long_sequence(sd3):
     m, _, (xx, cc), (x_ref, c_ref) = _block_case(sd3, 1, 16384, 333, seed=4, dual=False)
     assert rel_l2(xx, x_ref.cpu()) < 1e-2
     assert rel_l2(cc, c_ref.cpu()) < 1e-2
+    m.close()
+
+
+def test_model_golden_fp8_mode(sd3):
+    """FP8 mode: the block GEMMs take e4m3 operands (weights with one scale per
+    matrix, activations converted as they are), everything else as in the bf16
+    mode.  e4m3 keeps three mantissa bits, so the bar is 1e-1 on the toy model;
+    the bf16 mode on the same inputs is at 3e-3."""
+    g = golden("model_toy.pt")
+    m = make_model(sd3, g["config"], g["params"], sd3.PRECISION_FP8)
+    out = m.forward(g["pooled"].bfloat16().cuda(), g["captions"].bfloat16().cuda(),
+                    g["latent"].bfloat16().cuda(), g["timesteps"].cuda())
+    torch.cuda.synchronize()
+    assert sd3.device_status() == 0
+    r = rel_l2(out, g["out"])
+    print("fp8 toy rel_l2", r)
+    assert r < 1e-1
     m.close()
