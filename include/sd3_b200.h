@@ -47,7 +47,7 @@ extern "C" {
 /* precision modes of a model */
 #define SD3_PRECISION_BF16 0 /* bf16 tensor-core operands, fp32 accumulation / residual streams */
 #define SD3_PRECISION_F32 1  /* exact fp32 arithmetic (parity mode for fp32 tensors) */
-#define SD3_PRECISION_FP8 2  /* e4m3 per-tensor-scaled GEMM operands, bf16 attention */
+#define SD3_PRECISION_FP8 2  /* bf16 mode with the block GEMMs on e4m3 operands (one scale per weight matrix) */
 
 /* epilogues of sd3_linear */
 #define SD3_ACT_NONE 0

@@ -272,8 +272,10 @@ int reserve_ws(sd3_model* m, int B, int Tc, int Tx) {
   return ST_OK;
 }
 
+// a_e4m3: A already holds e4m3 bytes (FP8 mode: written by ln_modulate, the GELU
+// epilogue or a conversion pass)
 int run_linear(sd3_model* m, const Linear& L, const void* A, int M, const GemmEpilogue& e,
-               cudaStream_t st) {
+               cudaStream_t st, bool a_e4m3 = false) {
   if (!L.w) {
     set_last_error("a required weight is missing (N %d K %d)", L.N, L.K);
     return ST_NOT_READY;
@@ -287,10 +289,18 @@ int run_linear(sd3_model* m, const Linear& L, const void* A, int M, const GemmEp
     // e4m3 x e4m3: the bf16 operand is converted as is (scale 1: LayerNorm
     // outputs, attention outputs and GELU outputs sit well inside e4m3's range and
     // the conversion saturates), the weight's scale is undone in the epilogue.
-    int rc = launch_quantize_e4m3(A, 0, m->ws.a8, static_cast<long>(M) * L.K, 1.0f, st);
-    if (rc) return rc;
+    const void* a8 = A;
+    if (!a_e4m3) {
+      int rc = launch_quantize_e4m3(A, 0, m->ws.a8, static_cast<long>(M) * L.K, 1.0f, st);
+      if (rc) return rc;
+      a8 = m->ws.a8;
+    }
     ee.alpha = L.wscale;
-    return launch_gemm(m->ws.a8, L.K, L.w8, L.K, OPERAND_E4M3, M, L.N, L.K, ee, m->status, st);
+    return launch_gemm(a8, L.K, L.w8, L.K, OPERAND_E4M3, M, L.N, L.K, ee, m->status, st);
+  }
+  if (a_e4m3) {
+    set_last_error("an e4m3 operand reached a GEMM without e4m3 weights (N %d K %d)", L.N, L.K);
+    return ST_UNSUPPORTED;
   }
   return launch_gemm(A, L.K, L.w, L.K, OPERAND_BF16, M, L.N, L.K, ee, m->status, st);
 }
@@ -298,7 +308,7 @@ int run_linear(sd3_model* m, const Linear& L, const void* A, int M, const GemmEp
 // QKV projection of `T_in` tokens per sample into rows [row_off, row_off+T_in)
 // of each sample of the packed (B, T_total, 3E) buffer, q/k RMSNorm included.
 int run_qkv(sd3_model* m, const Linear& L, const void* h, void* qkv, int B, int T_in, int T_total,
-            int row_off, const float* wq, const float* wk, cudaStream_t st) {
+            int row_off, const float* wq, const float* wk, cudaStream_t st, bool h_e4m3 = false) {
   const int E = m->E;
   const bool norm = m->cfg.use_qk_norm && (wq || wk);
   const bool fused = !m->f32 && m->D == 64;
@@ -311,7 +321,7 @@ int run_qkv(sd3_model* m, const Linear& L, const void* h, void* qkv, int B, int 
   e.wq = wq; e.wk = wk; e.qk_cols = 2 * E; e.eps = 1e-6f;
   e.do_norm = (fused && norm) ? 1 : 0;
   if (!fused) e.qk_cols = 0;
-  int rc = run_linear(m, L, h, B * T_in, e, st);
+  int rc = run_linear(m, L, h, B * T_in, e, st, h_e4m3);
   if (rc || fused || !norm) return rc;
   const size_t ab = m->wbytes();
   for (int b = 0; b < B; ++b) {
@@ -338,20 +348,24 @@ int run_attention(sd3_model* m, const void* qkv, int B, int T, int Tc, void* o_c
 }
 
 int run_gate_resid(sd3_model* m, const Linear& L, const void* A, int B, int Tseg, const float* gate,
-                   long mod_stride, float* resid, cudaStream_t st) {
+                   long mod_stride, float* resid, cudaStream_t st, bool a_e4m3 = false) {
   GemmEpilogue e;
   e.mode = EPI_GATE_RESID;
   e.out = resid; e.resid = resid; e.out_f32 = 1; e.ldo = L.N;
   e.gate = gate; e.gate_stride = mod_stride;
   e.rows_in = Tseg; e.rows_out = Tseg; e.row_off = 0;
-  return run_linear(m, L, A, B * Tseg, e, st);
+  return run_linear(m, L, A, B * Tseg, e, st, a_e4m3);
 }
 
-int run_mlp1(sd3_model* m, const Linear& L, const void* A, int M, void* hid, cudaStream_t st) {
+// hid_e4m3 (out): whether the hidden activations were written as e4m3
+int run_mlp1(sd3_model* m, const Linear& L, const Linear& next, const void* A, int M, void* hid,
+             cudaStream_t st, bool a_e4m3, bool* hid_e4m3) {
   GemmEpilogue e;
   e.mode = EPI_BIAS_GELU;
   e.out = hid; e.out_f32 = m->f32; e.ldo = L.N;
-  return run_linear(m, L, A, M, e, st);
+  *hid_e4m3 = m->fp8 && L.w8 && next.w8 && L.N % 64 == 0;
+  e.out_e4m3 = *hid_e4m3 ? 1 : 0;
+  return run_linear(m, L, A, M, e, st, a_e4m3);
 }
 
 int block_body(sd3_model* m, int l, float* c, float* x, int B, int Tc, int Tx, const float* mod,
@@ -374,37 +388,43 @@ int block_body(sd3_model* m, int l, float* c, float* x, int B, int Tc, int Tx, c
   const float *x_shift_2 = xm + 6 * E, *x_scale_2 = xm + 7 * E, *x_gate_2 = xm + 8 * E;
   int rc;
 #define SD3_TRY(expr) do { rc = (expr); if (rc) return rc; } while (0)
+  // FP8 mode: LayerNorm writes the e4m3 operand of the following GEMM directly when
+  // that GEMM (and, for the dual output, its twin) has e4m3 weights.
+  const bool c8a = m->fp8 && L.c_qkv.w8, x8a = m->fp8 && L.x_qkv.w8 && (!L.dual || L.d_qkv.w8);
+  const bool c8m = m->fp8 && L.c_mlp1.w8, x8m = m->fp8 && L.x_mlp1.w8;
+  auto ln_out = [&](bool e4m3) { return m->f32 ? 1 : (e4m3 ? 2 : 0); };
   // pre-attention LayerNorm + modulate
   SD3_TRY(launch_ln_modulate(c, B, Tc, E, 1e-6f, c_shift_a, c_scale_a, w.h_c, nullptr, nullptr,
-                             nullptr, ms, m->f32, st));
+                             nullptr, ms, ln_out(c8a), st));
   if (L.dual)
     SD3_TRY(launch_ln_modulate(x, B, Tx, E, 1e-6f, x_shift_a, x_scale_a, w.h_x, x_shift_2, x_scale_2,
-                               w.h_x2, ms, m->f32, st));
+                               w.h_x2, ms, ln_out(x8a), st));
   else
     SD3_TRY(launch_ln_modulate(x, B, Tx, E, 1e-6f, x_shift_a, x_scale_a, w.h_x, nullptr, nullptr,
-                               nullptr, ms, m->f32, st));
+                               nullptr, ms, ln_out(x8a), st));
   // QKV (context rows first, then image rows) and joint attention
-  SD3_TRY(run_qkv(m, L.c_qkv, w.h_c, w.qkv, B, Tc, T, 0, L.c_wq, L.c_wk, st));
-  SD3_TRY(run_qkv(m, L.x_qkv, w.h_x, w.qkv, B, Tx, T, Tc, L.x_wq, L.x_wk, st));
+  SD3_TRY(run_qkv(m, L.c_qkv, w.h_c, w.qkv, B, Tc, T, 0, L.c_wq, L.c_wk, st, c8a));
+  SD3_TRY(run_qkv(m, L.x_qkv, w.h_x, w.qkv, B, Tx, T, Tc, L.x_wq, L.x_wk, st, x8a));
   SD3_TRY(run_attention(m, w.qkv, B, T, Tc, L.last ? nullptr : w.o_c, w.o_x, st));
   if (!L.last) SD3_TRY(run_gate_resid(m, L.c_out, w.o_c, B, Tc, c_gate_a, ms, c, st));
   SD3_TRY(run_gate_resid(m, L.x_out, w.o_x, B, Tx, x_gate_a, ms, x, st));
   if (L.dual) {
-    SD3_TRY(run_qkv(m, L.d_qkv, w.h_x2, w.qkv2, B, Tx, Tx, 0, L.d_wq, L.d_wk, st));
+    SD3_TRY(run_qkv(m, L.d_qkv, w.h_x2, w.qkv2, B, Tx, Tx, 0, L.d_wq, L.d_wk, st, x8a));
     SD3_TRY(run_attention(m, w.qkv2, B, Tx, 0, nullptr, w.o_x2, st));
     SD3_TRY(run_gate_resid(m, L.d_out, w.o_x2, B, Tx, x_gate_2, ms, x, st));
   }
   // image MLP
+  bool hid8 = false;
   SD3_TRY(launch_ln_modulate(x, B, Tx, E, 1e-6f, x_shift_m, x_scale_m, w.h_x, nullptr, nullptr,
-                             nullptr, ms, m->f32, st));
-  SD3_TRY(run_mlp1(m, L.x_mlp1, w.h_x, B * Tx, w.hid_x, st));
-  SD3_TRY(run_gate_resid(m, L.x_mlp2, w.hid_x, B, Tx, x_gate_m, ms, x, st));
+                             nullptr, ms, ln_out(x8m), st));
+  SD3_TRY(run_mlp1(m, L.x_mlp1, L.x_mlp2, w.h_x, B * Tx, w.hid_x, st, x8m, &hid8));
+  SD3_TRY(run_gate_resid(m, L.x_mlp2, w.hid_x, B, Tx, x_gate_m, ms, x, st, hid8));
   // context MLP
   if (!L.last) {
     SD3_TRY(launch_ln_modulate(c, B, Tc, E, 1e-6f, c_shift_m, c_scale_m, w.h_c, nullptr, nullptr,
-                               nullptr, ms, m->f32, st));
-    SD3_TRY(run_mlp1(m, L.c_mlp1, w.h_c, B * Tc, w.hid_c, st));
-    SD3_TRY(run_gate_resid(m, L.c_mlp2, w.hid_c, B, Tc, c_gate_m, ms, c, st));
+                               nullptr, ms, ln_out(c8m), st));
+    SD3_TRY(run_mlp1(m, L.c_mlp1, L.c_mlp2, w.h_c, B * Tc, w.hid_c, st, c8m, &hid8));
+    SD3_TRY(run_gate_resid(m, L.c_mlp2, w.hid_c, B, Tc, c_gate_m, ms, c, st, hid8));
   }
 #undef SD3_TRY
   return ST_OK;

@@ -192,6 +192,18 @@ __device__ __forceinline__ void epilogue_64(float (&v)[64], const RowMap& rm, in
     for (int j = 0; j < 64; ++j) v[j] += tt[j];
   }
   const long base = rm.orow * e.ldo;
+  if constexpr (!OUT_F32 && (EPI == EPI_BIAS || EPI == EPI_BIAS_GELU)) {
+    if (e.out_e4m3) {  // 64 bytes per thread; N % 64 == 0 is checked at launch
+      uint4* q = reinterpret_cast<uint4*>(static_cast<uint8_t*>(e.out) + base + n_base);
+#pragma unroll
+      for (int gi = 0; gi < 4; ++gi) {
+        const float* o = &v[gi * 16];
+        q[gi] = make_uint4(pack_e4m3x4(o[0], o[1], o[2], o[3]), pack_e4m3x4(o[4], o[5], o[6], o[7]),
+                           pack_e4m3x4(o[8], o[9], o[10], o[11]), pack_e4m3x4(o[12], o[13], o[14], o[15]));
+      }
+      return;
+    }
+  }
   if (n_base + 64 <= N) {
 #pragma unroll
     for (int gi = 0; gi < 4; ++gi)

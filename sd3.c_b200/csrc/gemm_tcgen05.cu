@@ -346,6 +346,11 @@ int launch_gemm(const void* A, long lda, const void* W, long ldw, int operand_dt
     set_last_error("gemm: operands must be 16-byte aligned with 16-byte-multiple row pitch");
     return ST_INVALID_ARG;
   }
+  if (epi.out_e4m3 && (epi.out_f32 || (epi.mode != EPI_BIAS && epi.mode != EPI_BIAS_GELU) || N % 64 != 0 ||
+                       epi.ldo % 16 != 0)) {
+    set_last_error("gemm: e4m3 output needs a bias or bias+GELU epilogue, N %% 64 == 0 and ldo %% 16 == 0");
+    return ST_INVALID_ARG;
+  }
   if (epi.mode != EPI_UNPATCHIFY) {
     const long oa = epi.out_f32 ? 4 : 8;
     if (N % 8 != 0 || epi.ldo % oa != 0 || (reinterpret_cast<uintptr_t>(epi.out) & 15)) {

@@ -45,6 +45,8 @@ struct GemmEpilogue {
   const float* bias = nullptr;  // [N] or null
   void* out = nullptr;
   int out_f32 = 0;              // 0: bf16 output, 1: fp32 output
+  int out_e4m3 = 0;             // with out_f32 == 0: one e4m3 byte per element (N % 64 == 0), the
+                                // operand of a following FP8 GEMM; BIAS and BIAS_GELU modes only
   long ldo = 0;                 // output leading dimension in elements
   // Row remap: GEMM row m belongs to sample b = m / rows_in and is written to
   // output row b * rows_out + row_off + (m % rows_in).  rows_in = 0 means no remap.
@@ -96,7 +98,8 @@ int launch_attention_simt(const void* q, const void* k, const void* v, long ld, 
 // Memory-bound kernels
 // ----------------------------------------------------------------------------
 // LayerNorm (no affine) + up to two modulations:  out_i = LN(x) * (1 + scale_i[b]) + shift_i[b]
-// x: (B*T, E) fp32.  shift/scale: [b * mod_stride + e].  out: bf16 or fp32 (out_f32).
+// x: (B*T, E) fp32.  shift/scale: [b * mod_stride + e].  out: bf16 (out_f32 = 0), fp32 (1) or
+// e4m3 converted as is (2).
 int launch_ln_modulate(const float* x, int B, int T, int E, float eps, const float* shift1,
                        const float* scale1, void* out1, const float* shift2, const float* scale2,
                        void* out2, long mod_stride, int out_f32, cudaStream_t stream);

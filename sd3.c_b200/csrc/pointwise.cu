@@ -22,7 +22,8 @@ namespace {
 // ----------------------------------------------------------------------------
 // LayerNorm + modulate.  One warp per row, the row lives in registers.
 // ----------------------------------------------------------------------------
-template <int MAXV, bool OUT_F32, bool DUAL>
+// OUT: 0 bf16, 1 fp32, 2 e4m3 (operand of an FP8 GEMM, converted as is)
+template <int MAXV, int OUT, bool DUAL>
 __global__ void __launch_bounds__(256, 4)
 ln_modulate_kernel(const float* __restrict__ x, long rows, int T, int E, float eps,
                    const float* __restrict__ shift1, const float* __restrict__ scale1,
@@ -77,8 +78,10 @@ ln_modulate_kernel(const float* __restrict__ x, long rows, int T, int E, float e
         o.y = fmaf(n.y, 1.f + s.y, h.y);
         o.z = fmaf(n.z, 1.f + s.z, h.z);
         o.w = fmaf(n.w, 1.f + s.w, h.w);
-        if constexpr (OUT_F32) {
+        if constexpr (OUT == 1) {
           reinterpret_cast<float4*>(static_cast<float*>(out1) + row * E)[i] = o;
+        } else if constexpr (OUT == 2) {
+          reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(out1) + row * E)[i] = pack_e4m3x4(o.x, o.y, o.z, o.w);
         } else {
           uint2 u;
           u.x = pack_bf16x2(o.x, o.y);
@@ -93,8 +96,10 @@ ln_modulate_kernel(const float* __restrict__ x, long rows, int T, int E, float e
         o.y = fmaf(n.y, 1.f + s.y, h.y);
         o.z = fmaf(n.z, 1.f + s.z, h.z);
         o.w = fmaf(n.w, 1.f + s.w, h.w);
-        if constexpr (OUT_F32) {
+        if constexpr (OUT == 1) {
           reinterpret_cast<float4*>(static_cast<float*>(out2) + row * E)[i] = o;
+        } else if constexpr (OUT == 2) {
+          reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(out2) + row * E)[i] = pack_e4m3x4(o.x, o.y, o.z, o.w);
         } else {
           uint2 u;
           u.x = pack_bf16x2(o.x, o.y);
@@ -116,10 +121,12 @@ int launch_ln_inst(const float* x, long rows, int T, int E, float eps, const flo
 #define SD3_LN_LAUNCH(F32, DUALV)                                                              \
   ln_modulate_kernel<MAXV, F32, DUALV><<<grid, wpb * 32, 0, stream>>>(                         \
       x, rows, T, E, eps, shift1, scale1, out1, shift2, scale2, out2, mod_stride)
-  if (out_f32) {
-    if (dual) SD3_LN_LAUNCH(true, true); else SD3_LN_LAUNCH(true, false);
+  if (out_f32 == 1) {
+    if (dual) SD3_LN_LAUNCH(1, true); else SD3_LN_LAUNCH(1, false);
+  } else if (out_f32 == 2) {
+    if (dual) SD3_LN_LAUNCH(2, true); else SD3_LN_LAUNCH(2, false);
   } else {
-    if (dual) SD3_LN_LAUNCH(false, true); else SD3_LN_LAUNCH(false, false);
+    if (dual) SD3_LN_LAUNCH(0, true); else SD3_LN_LAUNCH(0, false);
   }
 #undef SD3_LN_LAUNCH
   return after_launch("ln_modulate_kernel");
@@ -446,12 +453,6 @@ int launch_patchify(const void* latent, int in_f32, void* out, int out_f32, int 
 // nearest even; and the absolute maximum a scale is derived from.
 // ----------------------------------------------------------------------------
 namespace {
-
-__device__ __forceinline__ uint16_t pack_e4m3x2(float lo, float hi) {
-  uint16_t r;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
-  return r;
-}
 
 template <typename TI>
 __global__ void quantize_e4m3_kernel(const TI* __restrict__ in, uint8_t* __restrict__ out, long n,
