@@ -62,6 +62,7 @@ struct AttnArgs {
   bf16* out_c;
   bf16* out_x;
   float scale_log2e;
+  int out_e4m3;  // outputs are e4m3 bytes (operand of an FP8 out-projection) instead of bf16
   int* status;
   long long* probe;  // diagnostics (SD3_ATTN_PROBE=1): 8 counters per CTA, else null
 };
@@ -382,10 +383,38 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
       if (t < T) {
         const float inv = 1.0f / l;
         bf16* dst = nullptr;
+        long off = -1;  // element offset of this row's 64 values in out_c / out_x
         if (t < a.Tc) {
-          if (a.out_c) dst = a.out_c + (static_cast<long>(b) * a.Tc + t) * a.E + h * AT_D;
+          if (a.out_c) off = (static_cast<long>(b) * a.Tc + t) * a.E + h * AT_D;
         } else {
-          dst = a.out_x + (static_cast<long>(b) * (T - a.Tc) + (t - a.Tc)) * a.E + h * AT_D;
+          off = (static_cast<long>(b) * (T - a.Tc) + (t - a.Tc)) * a.E + h * AT_D;
+        }
+        if (off >= 0 && a.out_e4m3) {
+          uint4* d4 = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(t < a.Tc ? a.out_c : a.out_x) + off);
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            uint4 u, w;
+            u.x = pack_e4m3x4(__uint_as_float(o0[16 * i + 0]) * inv, __uint_as_float(o0[16 * i + 1]) * inv,
+                              __uint_as_float(o0[16 * i + 2]) * inv, __uint_as_float(o0[16 * i + 3]) * inv);
+            u.y = pack_e4m3x4(__uint_as_float(o0[16 * i + 4]) * inv, __uint_as_float(o0[16 * i + 5]) * inv,
+                              __uint_as_float(o0[16 * i + 6]) * inv, __uint_as_float(o0[16 * i + 7]) * inv);
+            u.z = pack_e4m3x4(__uint_as_float(o0[16 * i + 8]) * inv, __uint_as_float(o0[16 * i + 9]) * inv,
+                              __uint_as_float(o0[16 * i + 10]) * inv, __uint_as_float(o0[16 * i + 11]) * inv);
+            u.w = pack_e4m3x4(__uint_as_float(o0[16 * i + 12]) * inv, __uint_as_float(o0[16 * i + 13]) * inv,
+                              __uint_as_float(o0[16 * i + 14]) * inv, __uint_as_float(o0[16 * i + 15]) * inv);
+            w.x = pack_e4m3x4(__uint_as_float(o1[16 * i + 0]) * inv, __uint_as_float(o1[16 * i + 1]) * inv,
+                              __uint_as_float(o1[16 * i + 2]) * inv, __uint_as_float(o1[16 * i + 3]) * inv);
+            w.y = pack_e4m3x4(__uint_as_float(o1[16 * i + 4]) * inv, __uint_as_float(o1[16 * i + 5]) * inv,
+                              __uint_as_float(o1[16 * i + 6]) * inv, __uint_as_float(o1[16 * i + 7]) * inv);
+            w.z = pack_e4m3x4(__uint_as_float(o1[16 * i + 8]) * inv, __uint_as_float(o1[16 * i + 9]) * inv,
+                              __uint_as_float(o1[16 * i + 10]) * inv, __uint_as_float(o1[16 * i + 11]) * inv);
+            w.w = pack_e4m3x4(__uint_as_float(o1[16 * i + 12]) * inv, __uint_as_float(o1[16 * i + 13]) * inv,
+                              __uint_as_float(o1[16 * i + 14]) * inv, __uint_as_float(o1[16 * i + 15]) * inv);
+            d4[i] = u;
+            d4[2 + i] = w;
+          }
+        } else if (off >= 0) {
+          dst = (t < a.Tc ? a.out_c : a.out_x) + off;
         }
         if (dst) {
           uint4* d4 = reinterpret_cast<uint4*>(dst);
@@ -425,7 +454,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
 }  // namespace
 
 int launch_attention_bf16(const bf16* qkv, int B, int T, int NH, int Tc, bf16* out_c, bf16* out_x,
-                          float scale, int* dev_status, cudaStream_t stream) {
+                          float scale, int* dev_status, cudaStream_t stream, int out_e4m3) {
   if (!qkv || !out_x || B <= 0 || T <= 0 || NH <= 0 || Tc < 0 || Tc > T ||
       (reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(out_x) & 15) ||
       (reinterpret_cast<uintptr_t>(out_c) & 15)) {
@@ -457,6 +486,7 @@ int launch_attention_bf16(const bf16* qkv, int B, int T, int NH, int Tc, bf16* o
   a.B = B; a.T = T; a.NH = NH; a.Tc = Tc; a.E = E;
   a.out_c = out_c; a.out_x = out_x;
   a.scale_log2e = scale * 1.4426950408889634f;
+  a.out_e4m3 = out_e4m3;
   a.status = dev_status;
   a.probe = nullptr;
   const dim3 grid((T + AT_BM - 1) / AT_BM, NH, B);

@@ -334,13 +334,18 @@ int run_qkv(sd3_model* m, const Linear& L, const void* h, void* qkv, int B, int 
   return ST_OK;
 }
 
+// out_e4m3 (FP8 mode, head_dim 64 only): the outputs feed FP8 out-projections
 int run_attention(sd3_model* m, const void* qkv, int B, int T, int Tc, void* o_c, void* o_x,
-                  cudaStream_t st) {
+                  cudaStream_t st, bool out_e4m3 = false) {
   const float scale = 1.0f / sqrtf(static_cast<float>(m->D));
   if (!m->f32 && m->D == 64)
     return launch_attention_bf16(static_cast<const bf16*>(qkv), B, T, m->NH, Tc,
                                  static_cast<bf16*>(o_c), static_cast<bf16*>(o_x), scale, m->status,
-                                 st);
+                                 st, out_e4m3 ? 1 : 0);
+  if (out_e4m3) {
+    set_last_error("e4m3 attention output needs head_dim 64");
+    return ST_UNSUPPORTED;
+  }
   const size_t ab = m->wbytes();
   const char* q = static_cast<const char*>(qkv);
   return launch_attention_simt(q, q + m->E * ab, q + 2 * m->E * ab, 3L * m->E, m->f32, B, T, m->NH,
@@ -405,13 +410,17 @@ int block_body(sd3_model* m, int l, float* c, float* x, int B, int Tc, int Tx, c
   // QKV (context rows first, then image rows) and joint attention
   SD3_TRY(run_qkv(m, L.c_qkv, w.h_c, w.qkv, B, Tc, T, 0, L.c_wq, L.c_wk, st, c8a));
   SD3_TRY(run_qkv(m, L.x_qkv, w.h_x, w.qkv, B, Tx, T, Tc, L.x_wq, L.x_wk, st, x8a));
-  SD3_TRY(run_attention(m, w.qkv, B, T, Tc, L.last ? nullptr : w.o_c, w.o_x, st));
-  if (!L.last) SD3_TRY(run_gate_resid(m, L.c_out, w.o_c, B, Tc, c_gate_a, ms, c, st));
-  SD3_TRY(run_gate_resid(m, L.x_out, w.o_x, B, Tx, x_gate_a, ms, x, st));
+  // FP8 mode: both out-projections of the joint attention must take e4m3 for the
+  // kernel to write it (one flag for both outputs)
+  const bool o8 = m->fp8 && m->D == 64 && L.x_out.w8 && (L.last || L.c_out.w8);
+  SD3_TRY(run_attention(m, w.qkv, B, T, Tc, L.last ? nullptr : w.o_c, w.o_x, st, o8));
+  if (!L.last) SD3_TRY(run_gate_resid(m, L.c_out, w.o_c, B, Tc, c_gate_a, ms, c, st, o8));
+  SD3_TRY(run_gate_resid(m, L.x_out, w.o_x, B, Tx, x_gate_a, ms, x, st, o8));
   if (L.dual) {
     SD3_TRY(run_qkv(m, L.d_qkv, w.h_x2, w.qkv2, B, Tx, Tx, 0, L.d_wq, L.d_wk, st, x8a));
-    SD3_TRY(run_attention(m, w.qkv2, B, Tx, 0, nullptr, w.o_x2, st));
-    SD3_TRY(run_gate_resid(m, L.d_out, w.o_x2, B, Tx, x_gate_2, ms, x, st));
+    const bool o8d = m->fp8 && m->D == 64 && L.d_out.w8;
+    SD3_TRY(run_attention(m, w.qkv2, B, Tx, 0, nullptr, w.o_x2, st, o8d));
+    SD3_TRY(run_gate_resid(m, L.d_out, w.o_x2, B, Tx, x_gate_2, ms, x, st, o8d));
   }
   // image MLP
   bool hid8 = false;

@@ -85,8 +85,9 @@ int launch_gemm(const void* A, long lda, const void* W, long ldw, int operand_dt
 // Output row t of sample b goes to out_c[(b*Tc + t), :] for t < Tc, otherwise
 // to out_x[(b*(T-Tc) + t - Tc), :]; out_c may be null (context rows dropped).
 // ----------------------------------------------------------------------------
+// out_e4m3: out_c / out_x receive one e4m3 byte per element (rows E bytes apart) instead of bf16.
 int launch_attention_bf16(const bf16* qkv, int B, int T, int NH, int Tc, bf16* out_c, bf16* out_x,
-                          float scale, int* dev_status, cudaStream_t stream);
+                          float scale, int* dev_status, cudaStream_t stream, int out_e4m3 = 0);
 
 // Generic SIMT attention (any head_dim <= 128, fp32 or bf16 in, fp32 math).
 // q, k, v: row (b*T + t) at base + row*ld + h*D.  out rows split like above.
