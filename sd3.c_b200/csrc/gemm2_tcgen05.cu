@@ -50,12 +50,14 @@ constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 256 + 1024;
 
 // PROBE: cycle counters compiled in (diagnostic instantiation only; even behind a
 // runtime flag they slow the issue loops down).
-template <int EPI, bool OUT_F32, bool PROBE>
+template <int EPI, bool OUT_F32, bool PROBE, bool FP8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                          const __grid_constant__ CUtensorMap tmW, const GemmArgs g,
                          long long* __restrict__ probe, int skip_loads) {
-  constexpr uint32_t IDESC = make_idesc(1, 1, 2 * P_BM, P_BN, 0, 0);  // M = 256 across the pair
+  // M = 256 across the pair; operands bf16, or e4m3 (128 K-elements per 128-byte stage row,
+  // 32 per instruction: the byte arithmetic of the stages is the same)
+  constexpr uint32_t IDESC = FP8 ? make_idesc(0, 0, 2 * P_BM, P_BN, 0, 0) : make_idesc(1, 1, 2 * P_BM, P_BN, 0, 0);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -122,8 +124,9 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             if (rank == 0) mbar_arrive(&full_bar[stage]);  // experiment: reuse stale operands
           } else {
             if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * P_STAGE_BYTES);
-            tma_load_2d_pair(sa, &tmA, bar, kb * 64, m0);
-            tma_load_2d_pair(sa + P_A_BYTES, &tmW, bar, kb * 64, n0);
+            constexpr int KEL = FP8 ? P_KBYTES : P_KBYTES / 2;  // K elements per stage
+            tma_load_2d_pair(sa, &tmA, bar, kb * KEL, m0);
+            tma_load_2d_pair(sa + P_A_BYTES, &tmW, bar, kb * KEL, n0);
           }
         }
         if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
@@ -168,7 +171,10 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 #pragma unroll
             for (int k = 0; k < P_KBYTES / 32; ++k) {
               const uint64_t adv = static_cast<uint64_t>((k * 32) >> 4);
-              mma_f16_ss_pair(d_tmem, a_desc + adv, b_desc + adv, IDESC, (kb | k) != 0);
+              if constexpr (FP8)
+                mma_f8_ss_pair(d_tmem, a_desc + adv, b_desc + adv, IDESC, (kb | k) != 0);
+              else
+                mma_f16_ss_pair(d_tmem, a_desc + adv, b_desc + adv, IDESC, (kb | k) != 0);
             }
             mma_commit_pair(&empty_bar[stage], 3);          // frees the stage in both CTAs
             if (kb == KB - 1) mma_commit_pair(&tfull_bar[acc], 3);  // accumulator ready in both CTAs
@@ -229,11 +235,11 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   }
 }
 
-template <int EPI, bool OUT_F32>
+template <int EPI, bool OUT_F32, bool FP8 = false>
 int launch_pair_inst(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmArgs& g,
                      cudaStream_t stream) {
-  auto kern = gemm_pair_tcgen05_kernel<EPI, OUT_F32, false>;
-  auto kern_probe = gemm_pair_tcgen05_kernel<EPI, OUT_F32, true>;
+  auto kern = gemm_pair_tcgen05_kernel<EPI, OUT_F32, false, FP8>;
+  auto kern_probe = gemm_pair_tcgen05_kernel<EPI, OUT_F32, !FP8, FP8>;  // no probe build of the e4m3 kernels
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -258,7 +264,7 @@ int launch_pair_inst(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmA
     return (v && v[0] == '2') ? 1 : 0;
   }();
   long long* probe = nullptr;
-  if (probing && g.status) {  // never on the allocation-free entry point (no status word there)
+  if (probing && !FP8 && g.status) {  // never on the allocation-free entry point (no status word there)
     if (cudaMalloc(&probe, sizeof(long long) * 8 * 2 * pairs) != cudaSuccess) probe = nullptr;
     if (probe) cudaMemset(probe, 0, sizeof(long long) * 8 * 2 * pairs);
   }
@@ -290,17 +296,23 @@ int launch_pair_inst(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmA
 // of 256, enough rows to fill pair tiles).
 bool gemm_pair_supported(int operand_dtype, int M, int N, int K, const GemmEpilogue& epi) {
   (void)K;
-  if (operand_dtype != OPERAND_BF16) return false;
   if (N % P_BN != 0 || M < 2 * P_BM) return false;
   if (epi.mode == EPI_UNPATCHIFY) return false;
-  return true;
+  if (operand_dtype == OPERAND_E4M3) {
+    // e4m3 instantiations exist for the three epilogues of the block GEMMs
+    if (epi.mode == EPI_GATE_RESID) return epi.out_f32 != 0;
+    return (epi.mode == EPI_QKV_NORM || epi.mode == EPI_BIAS_GELU || epi.mode == EPI_BIAS) && !epi.out_f32;
+  }
+  return operand_dtype == OPERAND_BF16;
 }
 
-int launch_gemm_pair(const void* A, long lda, const void* W, long ldw, int M, int N, int K,
-                     const GemmEpilogue& epi, int* dev_status, cudaStream_t stream) {
+int launch_gemm_pair(const void* A, long lda, const void* W, long ldw, int operand_dtype, int M, int N,
+                     int K, const GemmEpilogue& epi, int* dev_status, cudaStream_t stream) {
+  const bool fp8 = operand_dtype == OPERAND_E4M3;
+  const int eb = fp8 ? 1 : 2, kel = P_KBYTES / eb;  // element bytes, K elements per stage
   GemmArgs g;
   g.M = M; g.N = N; g.K = K;
-  g.k_blocks = (K + 63) / 64;
+  g.k_blocks = (K + kel - 1) / kel;
   g.tiles_m = (M + 2 * P_BM - 1) / (2 * P_BM);
   g.tiles_n = N / P_BN;
   g.epi = epi;
@@ -311,11 +323,22 @@ int launch_gemm_pair(const void* A, long lda, const void* W, long ldw, int M, in
                    ((reinterpret_cast<uintptr_t>(epi.out) & 31) == 0);
   }
   CUtensorMap tmA, tmW;
-  int rc = encode_tmap_2d(&tmA, A, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, 64, P_BM);
+  int rc = encode_tmap_2d(&tmA, A, eb, (uint64_t)K, (uint64_t)M, (uint64_t)lda * eb, kel, P_BM);
   if (rc) return rc;
-  rc = encode_tmap_2d(&tmW, W, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldw * 2, 64, P_BN_HALF);
+  rc = encode_tmap_2d(&tmW, W, eb, (uint64_t)K, (uint64_t)N, (uint64_t)ldw * eb, kel, P_BN_HALF);
   if (rc) return rc;
   const bool f32 = epi.out_f32 != 0;
+  if (fp8) {
+    switch (epi.mode) {
+      case EPI_BIAS: return launch_pair_inst<EPI_BIAS, false, true>(tmA, tmW, g, stream);
+      case EPI_BIAS_GELU: return launch_pair_inst<EPI_BIAS_GELU, false, true>(tmA, tmW, g, stream);
+      case EPI_QKV_NORM: return launch_pair_inst<EPI_QKV_NORM, false, true>(tmA, tmW, g, stream);
+      case EPI_GATE_RESID: return launch_pair_inst<EPI_GATE_RESID, true, true>(tmA, tmW, g, stream);
+      default: break;
+    }
+    set_last_error("gemm_pair: no e4m3 instantiation for epilogue mode %d", epi.mode);
+    return ST_UNSUPPORTED;
+  }
   switch (epi.mode) {
     case EPI_BIAS:
       return f32 ? launch_pair_inst<EPI_BIAS, true>(tmA, tmW, g, stream)

@@ -331,8 +331,8 @@ int dispatch_epi(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmArgs&
 }  // namespace
 
 bool gemm_pair_supported(int operand_dtype, int M, int N, int K, const GemmEpilogue& epi);
-int launch_gemm_pair(const void* A, long lda, const void* W, long ldw, int M, int N, int K,
-                     const GemmEpilogue& epi, int* dev_status, cudaStream_t stream);
+int launch_gemm_pair(const void* A, long lda, const void* W, long ldw, int operand_dtype, int M, int N,
+                     int K, const GemmEpilogue& epi, int* dev_status, cudaStream_t stream);
 
 int launch_gemm(const void* A, long lda, const void* W, long ldw, int operand_dtype, int M, int N,
                 int K, const GemmEpilogue& epi, int* dev_status, cudaStream_t stream) {
@@ -382,7 +382,7 @@ int launch_gemm(const void* A, long lda, const void* W, long ldw, int operand_dt
     return !(v && v[0] == '0');
   }();
   if (pair_enabled && gemm_pair_supported(operand_dtype, M, N, K, epi))
-    return launch_gemm_pair(A, lda, W, ldw, M, N, K, epi, dev_status, stream);
+    return launch_gemm_pair(A, lda, W, ldw, operand_dtype, M, N, K, epi, dev_status, stream);
 
   const int BN = (N >= 256 && N % 256 == 0) ? 256 : (N > 64 ? 128 : 64);
   const int elems_per_stage = STAGE_K_BYTES / eb;

@@ -238,3 +238,24 @@ def test_linear_e4m3_matches_the_same_contraction_in_fp32(sd3, M, N, K, act):
         ref = torch.nn.functional.gelu(ref, approximate="tanh")
     err = (out.double() - ref).abs().max().item()
     assert err < 2e-3 * max(1.0, ref.abs().max().item()), err
+
+
+@pytest.mark.parametrize("M,N,K,act", [(512, 256, 256, 0), (1024, 4608, 1536, 0), (333, 1536, 6144, 1)])
+def test_linear_e4m3_cta_pair_kernel_bf16_output(sd3, M, N, K, act):
+    """bf16 output with N % 256 == 0 and M >= 256 takes the CTA-pair e4m3 kernel."""
+    gen = torch.Generator(device="cuda").manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=gen, device="cuda")
+    w = torch.randn(N, K, generator=gen, device="cuda") * 0.02
+    bias = torch.randn(N, generator=gen, device="cuda") * 0.1
+    sx, sw = x.abs().max().item() / 448.0, w.abs().max().item() / 448.0
+    x8, w8 = (x / sx).to(torch.float8_e4m3fn), (w / sw).to(torch.float8_e4m3fn)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    sd3.check(sd3.lib().sd3_linear_e4m3(sd3.ptr(x8.view(torch.uint8)), sd3.ptr(w8.view(torch.uint8)),
+                                        sd3.ptr(bias), sd3.ptr(out), sd3.DTYPE_BF16, M, N, K, sx * sw, act,
+                                        sd3.stream_ptr()))
+    torch.cuda.synchronize()
+    assert sd3.device_status() == 0
+    ref = (x8.double() @ w8.double().t()) * (sx * sw) + bias.double()
+    if act:
+        ref = torch.nn.functional.gelu(ref, approximate="tanh")
+    assert ((out.double() - ref).norm() / ref.norm()).item() < 4e-3  # bf16 rounding of the output
