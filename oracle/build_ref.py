@@ -12,7 +12,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
-REF = os.environ.get("SD3_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: SD3_REFERENCE_ROOT, else a directory "reference" next to this repository
+REF = os.environ.get("SD3_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 STUB = r"""
 #include <torch/extension.h>

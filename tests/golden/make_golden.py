@@ -91,7 +91,9 @@ def make_model(ref, name, seed, num_layers, dual_layers, in_dim, E, pooled_dim, 
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    # the reference checkout: first argument, else a directory "reference" next to this repository
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.path.join(
+        os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference")
     sys.path.insert(0, os.path.join(ref_root, "module_tests"))
     import modules as ref  # the reference's PyTorch modules
 
