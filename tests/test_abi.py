@@ -45,3 +45,32 @@ def test_host_side_argument_errors_need_no_gpu():
     h = ctypes.c_void_p()
     assert lib.sd3_model_create(ctypes.byref(cfg), ctypes.byref(h)) == -1  # num_layers 0
     assert lib.sd3_cast(None, 0, None, 1, 4, None) == -1
+
+
+def test_bench_flop_accounting_matches_the_model_shapes():
+    """bench.py's STEP_TFLOP (algorithmic work of one config-3 step: 2MNK per GEMM,
+    4 T^2 E per attention, nothing else) recomputed from the model's shapes."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench_mod", os.path.join(REPO, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    B, Tc, Tx, E, F, L, dual = 8, 333, 4096, 1536, 6144, 24, 13
+    T = Tc + Tx
+    fl = 0.0
+    for l in range(L):
+        last = l == L - 1
+        rows_c, rows_x = B * Tc, B * Tx
+        fl += 2.0 * rows_c * E * 3 * E + 2.0 * rows_x * E * 3 * E            # QKV
+        fl += 4.0 * B * T * T * E                                          # joint attention
+        fl += 2.0 * rows_x * E * E + (0 if last else 2.0 * rows_c * E * E)  # out-proj
+        fl += 2 * 2.0 * rows_x * E * F + (0 if last else 2 * 2.0 * rows_c * E * F)  # MLP
+        if l < dual:
+            fl += 2.0 * rows_x * E * 3 * E + 4.0 * B * Tx * Tx * E + 2.0 * rows_x * E * E
+        chunks = (2 if last else 6) + (9 if l < dual else 6)
+        fl += 2.0 * B * E * chunks * E                                     # AdaLN
+    fl += 2.0 * B * E * 2 * E                                              # final AdaLN
+    fl += 2.0 * B * Tc * 4096 * E + 2.0 * B * Tx * 64 * E                  # caption projection, patch embed
+    fl += 2.0 * B * (256 * E + E * E + 2048 * E + E * E)                   # conditioning MLPs
+    fl += 2.0 * B * Tx * E * 64                                            # final linear
+    assert abs(fl / 1e12 - bench.STEP_TFLOP) < 0.01 * bench.STEP_TFLOP
+    assert bench.ATTN_TRAFFIC_BYTES_PER_SAMPLE > 4429 * 4608 * 2           # at least the q|k|v read
