@@ -259,3 +259,37 @@ def test_linear_e4m3_cta_pair_kernel_bf16_output(sd3, M, N, K, act):
     if act:
         ref = torch.nn.functional.gelu(ref, approximate="tanh")
     assert ((out.double() - ref).norm() / ref.norm()).item() < 4e-3  # bf16 rounding of the output
+
+
+@pytest.mark.parametrize("T", [63, 64, 65, 127, 128, 129, 191, 192, 193, 255, 256, 257, 320, 321])
+def test_attention_bf16_around_tile_boundaries(sd3, T):
+    """One to six 64-key sub-tiles, ragged and exact, through the three-buffer score ring."""
+    torch.manual_seed(T)
+    B, NH = 2, 2
+    Tc = T // 3
+    E = NH * 64
+    qkv = torch.randn(B, T, 3 * E, device="cuda").bfloat16()
+    oc, ox = sd3.attention(qkv, B, T, NH, Tc, 0.125)
+    q, k, v = [t.view(B, T, NH, 64).transpose(1, 2).float() for t in qkv.chunk(3, -1)]
+    ref = torch.nn.functional.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, T, E)
+    assert rel_l2(torch.cat([oc, ox], 1), ref) < 1e-2
+    assert sd3.device_status() == 0
+
+
+def test_attention_rising_scores_rescale_every_sub_tile(sd3):
+    """Scores that grow steadily along the keys move the running maximum by more
+    than 2^8 (exp2 domain) in every sub-tile, so O is rescaled each time."""
+    B, T, NH = 1, 512, 1
+    q = torch.zeros(B, T, 64, device="cuda")
+    q[..., 0] = 8.0
+    k = torch.zeros(B, T, 64, device="cuda")
+    k[..., 0] = torch.arange(T, device="cuda", dtype=torch.float32) * 0.25  # score*scale rises 0.25 per key
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    v = torch.randn(B, T, 64, generator=gen, device="cuda")
+    qkv = torch.cat([q, k, v], -1).bfloat16()
+    _, ox = sd3.attention(qkv, B, T, NH, 0, 0.125)
+    qf, kf, vf = [t.float().view(B, T, 1, 64).transpose(1, 2) for t in qkv.chunk(3, -1)]
+    ref = torch.nn.functional.scaled_dot_product_attention(qf, kf, vf).transpose(1, 2).reshape(B, T, 64)
+    assert torch.isfinite(ox.float()).all()
+    assert rel_l2(ox, ref) < 1e-2
+    assert sd3.device_status() == 0
