@@ -23,88 +23,130 @@ namespace {
 // LayerNorm + modulate.  One warp per row, the row lives in registers.
 // ----------------------------------------------------------------------------
 // OUT: 0 bf16, 1 fp32, 2 e4m3 (operand of an FP8 GEMM, converted as is)
+//
+// A CTA of 8 warps owns LN_ROWS_PER_CTA consecutive rows (8 per warp).  The
+// modulation vectors (1 + scale, shift; two pairs for DUAL) of the sample its
+// first row belongs to are staged in shared memory once: re-reading them from
+// global memory for every row (12 KB per 6 KB row, all L1 hits) cost a quarter
+// of the kernel's bandwidth.  Rows of another sample (a CTA that straddles a
+// sample boundary) read theirs from global memory.
+constexpr int LN_ROWS_PER_WARP = 8;
+constexpr int LN_WARPS = 8;
+constexpr int LN_ROWS_PER_CTA = LN_ROWS_PER_WARP * LN_WARPS;
+
+template <int OUT>
+__device__ __forceinline__ void ln_store4(void* out, long row, int E, int i, const float4& o) {
+  if constexpr (OUT == 1) {
+    reinterpret_cast<float4*>(static_cast<float*>(out) + row * E)[i] = o;
+  } else if constexpr (OUT == 2) {
+    reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(out) + row * E)[i] = pack_e4m3x4(o.x, o.y, o.z, o.w);
+  } else {
+    uint2 u;
+    u.x = pack_bf16x2(o.x, o.y);
+    u.y = pack_bf16x2(o.z, o.w);
+    reinterpret_cast<uint2*>(static_cast<bf16*>(out) + row * E)[i] = u;
+  }
+}
+
 template <int MAXV, int OUT, bool DUAL>
-__global__ void __launch_bounds__(256, 4)
+__global__ void __launch_bounds__(LN_WARPS * 32, 4)
 ln_modulate_kernel(const float* __restrict__ x, long rows, int T, int E, float eps,
                    const float* __restrict__ shift1, const float* __restrict__ scale1,
                    void* __restrict__ out1, const float* __restrict__ shift2,
                    const float* __restrict__ scale2, void* __restrict__ out2, long mod_stride) {
+  extern __shared__ float4 ln_smem[];  // [1 + scale1 | shift1 | 1 + scale2 | shift2], E floats each
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long row = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + warp;
-  if (row >= rows) return;
-  const int b = static_cast<int>(row / T);
   const int nvec = E >> 2;
-  const float4* xr = reinterpret_cast<const float4*>(x + row * E);
-  float4 v[MAXV];
-  float sum = 0.f;
-#pragma unroll
-  for (int j = 0; j < MAXV; ++j) {
-    const int i = lane + 32 * j;
-    if (i < nvec) {
-      v[j] = xr[i];
-      sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
-    } else {
-      v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+  const long row0 = static_cast<long>(blockIdx.x) * LN_ROWS_PER_CTA;
+  const int b_cta = static_cast<int>(row0 / T);
+  float4* s_sc1 = ln_smem;
+  float4* s_sh1 = ln_smem + nvec;
+  float4* s_sc2 = ln_smem + 2 * nvec;
+  float4* s_sh2 = ln_smem + 3 * nvec;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    float4 s = __ldg(reinterpret_cast<const float4*>(scale1 + b_cta * mod_stride) + i);
+    s.x += 1.f; s.y += 1.f; s.z += 1.f; s.w += 1.f;
+    s_sc1[i] = s;
+    s_sh1[i] = __ldg(reinterpret_cast<const float4*>(shift1 + b_cta * mod_stride) + i);
+    if constexpr (DUAL) {
+      float4 s2 = __ldg(reinterpret_cast<const float4*>(scale2 + b_cta * mod_stride) + i);
+      s2.x += 1.f; s2.y += 1.f; s2.z += 1.f; s2.w += 1.f;
+      s_sc2[i] = s2;
+      s_sh2[i] = __ldg(reinterpret_cast<const float4*>(shift2 + b_cta * mod_stride) + i);
     }
   }
-  const float mean = warp_sum(sum) / static_cast<float>(E);
-  float sq = 0.f;
+  __syncthreads();
+#pragma unroll 1
+  for (int rw = 0; rw < LN_ROWS_PER_WARP; ++rw) {
+    const long row = row0 + static_cast<long>(rw) * LN_WARPS + warp;  // warps interleave rows
+    if (row >= rows) break;
+    const int b = static_cast<int>(row / T);
+    const float4* xr = reinterpret_cast<const float4*>(x + row * E);
+    float4 v[MAXV];
+    float sum = 0.f;
 #pragma unroll
-  for (int j = 0; j < MAXV; ++j) {
-    const int i = lane + 32 * j;
-    if (i < nvec) {
-      const float a = v[j].x - mean, bq = v[j].y - mean, c = v[j].z - mean, d = v[j].w - mean;
-      sq += (a * a + bq * bq) + (c * c + d * d);
-    }
-  }
-  const float rstd = rsqrtf(warp_sum(sq) / static_cast<float>(E) + eps);
-  const float4* sh1 = reinterpret_cast<const float4*>(shift1 + b * mod_stride);
-  const float4* sc1 = reinterpret_cast<const float4*>(scale1 + b * mod_stride);
-  const float4* sh2 = DUAL ? reinterpret_cast<const float4*>(shift2 + b * mod_stride) : nullptr;
-  const float4* sc2 = DUAL ? reinterpret_cast<const float4*>(scale2 + b * mod_stride) : nullptr;
-#pragma unroll
-  for (int j = 0; j < MAXV; ++j) {
-    const int i = lane + 32 * j;
-    if (i < nvec) {
-      float4 n;
-      n.x = (v[j].x - mean) * rstd;
-      n.y = (v[j].y - mean) * rstd;
-      n.z = (v[j].z - mean) * rstd;
-      n.w = (v[j].w - mean) * rstd;
-      {
-        const float4 s = __ldg(sc1 + i), h = __ldg(sh1 + i);
-        float4 o;
-        o.x = fmaf(n.x, 1.f + s.x, h.x);
-        o.y = fmaf(n.y, 1.f + s.y, h.y);
-        o.z = fmaf(n.z, 1.f + s.z, h.z);
-        o.w = fmaf(n.w, 1.f + s.w, h.w);
-        if constexpr (OUT == 1) {
-          reinterpret_cast<float4*>(static_cast<float*>(out1) + row * E)[i] = o;
-        } else if constexpr (OUT == 2) {
-          reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(out1) + row * E)[i] = pack_e4m3x4(o.x, o.y, o.z, o.w);
-        } else {
-          uint2 u;
-          u.x = pack_bf16x2(o.x, o.y);
-          u.y = pack_bf16x2(o.z, o.w);
-          reinterpret_cast<uint2*>(static_cast<bf16*>(out1) + row * E)[i] = u;
-        }
+    for (int j = 0; j < MAXV; ++j) {
+      const int i = lane + 32 * j;
+      if (i < nvec) {
+        v[j] = xr[i];
+        sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+      } else {
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
       }
-      if constexpr (DUAL) {
-        const float4 s = __ldg(sc2 + i), h = __ldg(sh2 + i);
-        float4 o;
-        o.x = fmaf(n.x, 1.f + s.x, h.x);
-        o.y = fmaf(n.y, 1.f + s.y, h.y);
-        o.z = fmaf(n.z, 1.f + s.z, h.z);
-        o.w = fmaf(n.w, 1.f + s.w, h.w);
-        if constexpr (OUT == 1) {
-          reinterpret_cast<float4*>(static_cast<float*>(out2) + row * E)[i] = o;
-        } else if constexpr (OUT == 2) {
-          reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(out2) + row * E)[i] = pack_e4m3x4(o.x, o.y, o.z, o.w);
-        } else {
-          uint2 u;
-          u.x = pack_bf16x2(o.x, o.y);
-          u.y = pack_bf16x2(o.z, o.w);
-          reinterpret_cast<uint2*>(static_cast<bf16*>(out2) + row * E)[i] = u;
+    }
+    const float mean = warp_sum(sum) / static_cast<float>(E);
+    float sq = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+      const int i = lane + 32 * j;
+      if (i < nvec) {
+        const float a = v[j].x - mean, bq = v[j].y - mean, c = v[j].z - mean, d = v[j].w - mean;
+        sq += (a * a + bq * bq) + (c * c + d * d);
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(sq) / static_cast<float>(E) + eps);
+    const bool cached = b == b_cta;  // warp-uniform
+    const long moff = static_cast<long>(b) * mod_stride;  // used by rows of another sample only
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+      const int i = lane + 32 * j;
+      if (i < nvec) {
+        float4 n;
+        n.x = (v[j].x - mean) * rstd;
+        n.y = (v[j].y - mean) * rstd;
+        n.z = (v[j].z - mean) * rstd;
+        n.w = (v[j].w - mean) * rstd;
+        {
+          float4 s, h;
+          if (cached) {
+            s = s_sc1[i]; h = s_sh1[i];
+          } else {
+            s = __ldg(reinterpret_cast<const float4*>(scale1 + moff) + i);
+            h = __ldg(reinterpret_cast<const float4*>(shift1 + moff) + i);
+            s.x += 1.f; s.y += 1.f; s.z += 1.f; s.w += 1.f;
+          }
+          float4 o;
+          o.x = fmaf(n.x, s.x, h.x);
+          o.y = fmaf(n.y, s.y, h.y);
+          o.z = fmaf(n.z, s.z, h.z);
+          o.w = fmaf(n.w, s.w, h.w);
+          ln_store4<OUT>(out1, row, E, i, o);
+        }
+        if constexpr (DUAL) {
+          float4 s, h;
+          if (cached) {
+            s = s_sc2[i]; h = s_sh2[i];
+          } else {
+            s = __ldg(reinterpret_cast<const float4*>(scale2 + moff) + i);
+            h = __ldg(reinterpret_cast<const float4*>(shift2 + moff) + i);
+            s.x += 1.f; s.y += 1.f; s.z += 1.f; s.w += 1.f;
+          }
+          float4 o;
+          o.x = fmaf(n.x, s.x, h.x);
+          o.y = fmaf(n.y, s.y, h.y);
+          o.z = fmaf(n.z, s.z, h.z);
+          o.w = fmaf(n.w, s.w, h.w);
+          ln_store4<OUT>(out2, row, E, i, o);
         }
       }
     }
@@ -115,11 +157,11 @@ template <int MAXV>
 int launch_ln_inst(const float* x, long rows, int T, int E, float eps, const float* shift1,
                    const float* scale1, void* out1, const float* shift2, const float* scale2,
                    void* out2, long mod_stride, int out_f32, cudaStream_t stream) {
-  const int wpb = 8;
-  const unsigned grid = static_cast<unsigned>((rows + wpb - 1) / wpb);
+  const unsigned grid = static_cast<unsigned>((rows + LN_ROWS_PER_CTA - 1) / LN_ROWS_PER_CTA);
   const bool dual = out2 != nullptr;
+  const size_t smem = static_cast<size_t>(E) * 4 * (dual ? 4 : 2);
 #define SD3_LN_LAUNCH(F32, DUALV)                                                              \
-  ln_modulate_kernel<MAXV, F32, DUALV><<<grid, wpb * 32, 0, stream>>>(                         \
+  ln_modulate_kernel<MAXV, F32, DUALV><<<grid, LN_WARPS * 32, smem, stream>>>(                   \
       x, rows, T, E, eps, shift1, scale1, out1, shift2, scale2, out2, mod_stride)
   if (out_f32 == 1) {
     if (dual) SD3_LN_LAUNCH(1, true); else SD3_LN_LAUNCH(1, false);
