@@ -24,15 +24,15 @@ namespace {
 // ----------------------------------------------------------------------------
 // OUT: 0 bf16, 1 fp32, 2 e4m3 (operand of an FP8 GEMM, converted as is)
 //
-// A CTA of 8 warps owns LN_ROWS_PER_CTA consecutive rows (8 per warp).  The
+// A CTA of 8 warps owns 8 * rpw consecutive rows (rpw per warp, at most 8; fewer
+// for small inputs so that the grid still covers the GPU).  The
 // modulation vectors (1 + scale, shift; two pairs for DUAL) of the sample its
 // first row belongs to are staged in shared memory once: re-reading them from
 // global memory for every row (12 KB per 6 KB row, all L1 hits) cost a quarter
 // of the kernel's bandwidth.  Rows of another sample (a CTA that straddles a
 // sample boundary) read theirs from global memory.
-constexpr int LN_ROWS_PER_WARP = 8;
+constexpr int LN_MAX_ROWS_PER_WARP = 8;
 constexpr int LN_WARPS = 8;
-constexpr int LN_ROWS_PER_CTA = LN_ROWS_PER_WARP * LN_WARPS;
 
 template <int OUT>
 __device__ __forceinline__ void ln_store4(void* out, long row, int E, int i, const float4& o) {
@@ -53,11 +53,12 @@ __global__ void __launch_bounds__(LN_WARPS * 32, 4)
 ln_modulate_kernel(const float* __restrict__ x, long rows, int T, int E, float eps,
                    const float* __restrict__ shift1, const float* __restrict__ scale1,
                    void* __restrict__ out1, const float* __restrict__ shift2,
-                   const float* __restrict__ scale2, void* __restrict__ out2, long mod_stride) {
+                   const float* __restrict__ scale2, void* __restrict__ out2, long mod_stride,
+                   int rpw) {
   extern __shared__ float4 ln_smem[];  // [1 + scale1 | shift1 | 1 + scale2 | shift2], E floats each
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nvec = E >> 2;
-  const long row0 = static_cast<long>(blockIdx.x) * LN_ROWS_PER_CTA;
+  const long row0 = static_cast<long>(blockIdx.x) * (LN_WARPS * rpw);
   const int b_cta = static_cast<int>(row0 / T);
   float4* s_sc1 = ln_smem;
   float4* s_sh1 = ln_smem + nvec;
@@ -77,7 +78,7 @@ ln_modulate_kernel(const float* __restrict__ x, long rows, int T, int E, float e
   }
   __syncthreads();
 #pragma unroll 1
-  for (int rw = 0; rw < LN_ROWS_PER_WARP; ++rw) {
+  for (int rw = 0; rw < rpw; ++rw) {
     const long row = row0 + static_cast<long>(rw) * LN_WARPS + warp;  // warps interleave rows
     if (row >= rows) break;
     const int b = static_cast<int>(row / T);
@@ -157,12 +158,15 @@ template <int MAXV>
 int launch_ln_inst(const float* x, long rows, int T, int E, float eps, const float* shift1,
                    const float* scale1, void* out1, const float* shift2, const float* scale2,
                    void* out2, long mod_stride, int out_f32, cudaStream_t stream) {
-  const unsigned grid = static_cast<unsigned>((rows + LN_ROWS_PER_CTA - 1) / LN_ROWS_PER_CTA);
+  // rows per warp: as many as keeps at least two CTAs per SM busy
+  int rpw = LN_MAX_ROWS_PER_WARP;
+  while (rpw > 1 && (rows + LN_WARPS * rpw - 1) / (LN_WARPS * rpw) < 2L * 148) rpw >>= 1;
+  const unsigned grid = static_cast<unsigned>((rows + LN_WARPS * rpw - 1) / (LN_WARPS * rpw));
   const bool dual = out2 != nullptr;
   const size_t smem = static_cast<size_t>(E) * 4 * (dual ? 4 : 2);
 #define SD3_LN_LAUNCH(F32, DUALV)                                                              \
   ln_modulate_kernel<MAXV, F32, DUALV><<<grid, LN_WARPS * 32, smem, stream>>>(                   \
-      x, rows, T, E, eps, shift1, scale1, out1, shift2, scale2, out2, mod_stride)
+      x, rows, T, E, eps, shift1, scale1, out1, shift2, scale2, out2, mod_stride, rpw)
   if (out_f32 == 1) {
     if (dual) SD3_LN_LAUNCH(1, true); else SD3_LN_LAUNCH(1, false);
   } else if (out_f32 == 2) {
