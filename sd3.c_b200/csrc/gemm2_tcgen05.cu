@@ -43,18 +43,25 @@ constexpr int P_KBYTES = 128;        // bytes of K per stage row (64 bf16)
 constexpr int P_A_BYTES = P_BM * P_KBYTES;
 constexpr int P_B_BYTES = P_BN_HALF * P_KBYTES;
 constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;  // 32 KiB
-constexpr int P_STAGES = 7;
+// Stages of the operand ring: seven of 32 KiB, or six where the epilogue needs shared
+// memory of its own (gate + residual: 4 KiB per epilogue warp for the TMA reduction).
+constexpr int P_RED_BYTES = 4096;
+__host__ __device__ constexpr int pair_stages(int epi) { return epi == EPI_GATE_RESID ? 6 : 7; }
+__host__ __device__ constexpr int pair_red_bytes(int epi) { return epi == EPI_GATE_RESID ? EPI_WARPS * P_RED_BYTES : 0; }
 constexpr int P_TMEM_COLS = 512;     // two accumulators of 256 columns
 constexpr int P_THREADS = 64 + 32 * EPI_WARPS;
-constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 256 + 1024;
+__host__ __device__ constexpr int pair_smem_bytes(int epi) {
+  return pair_stages(epi) * P_STAGE_BYTES + pair_red_bytes(epi) + 256 + 1024;
+}
 
 // PROBE: cycle counters compiled in (diagnostic instantiation only; even behind a
 // runtime flag they slow the issue loops down).
 template <int EPI, bool OUT_F32, bool PROBE, bool FP8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
-                         const __grid_constant__ CUtensorMap tmW, const GemmArgs g,
-                         long long* __restrict__ probe, int skip_loads) {
+                         const __grid_constant__ CUtensorMap tmW,
+                         const __grid_constant__ CUtensorMap tmR,  // fp32 residual, gate + residual epilogue only
+                         const GemmArgs g, long long* __restrict__ probe, int skip_loads) {
   // M = 256 across the pair; operands bf16, or e4m3 (128 K-elements per 128-byte stage row,
   // 32 per instruction: the byte arithmetic of the stages is the same)
   constexpr uint32_t IDESC = FP8 ? make_idesc(0, 0, 2 * P_BM, P_BN, 0, 0) : make_idesc(1, 1, 2 * P_BM, P_BN, 0, 0);
@@ -62,7 +69,9 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + P_STAGES * P_STAGE_BYTES);
+  constexpr int P_STAGES = pair_stages(EPI);
+  uint8_t* red_smem = smem + P_STAGES * P_STAGE_BYTES;  // 1024-byte aligned: stages are 32 KiB each
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + P_STAGES * P_STAGE_BYTES + pair_red_bytes(EPI));
   uint64_t* empty_bar = full_bar + P_STAGES;
   uint64_t* tfull_bar = empty_bar + P_STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
@@ -206,15 +215,24 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                              static_cast<uint32_t>(acc * P_BN);
       const long long c0 = (PROBE && probe) ? clock64() : 0;
-      if (!drain_tile<P_BN, EPI, OUT_F32>(t_row, m0 + row, n0, half, g, &tfull_bar[acc], acc_phase, wc,
-                                          (PROBE && probe) ? w_epi : nullptr))
-        break;
+      bool drained;
+      if constexpr (EPI == EPI_GATE_RESID)
+        drained = drain_tile_gate_reduce<P_BN>(t_row, m0 + quad * 32, n0, half, g, &tmR, &tfull_bar[acc],
+                                               acc_phase, wc, red_smem + (warp - 2) * P_RED_BYTES,
+                                               (PROBE && probe) ? w_epi : nullptr);
+      else
+        drained = drain_tile<P_BN, EPI, OUT_F32>(t_row, m0 + row, n0, half, g, &tfull_bar[acc], acc_phase, wc,
+                                                 (PROBE && probe) ? w_epi : nullptr);
+      if (!drained) break;
       if (PROBE && probe) t_epi += clock64() - c0;  // includes the wait for the accumulator
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
+    }
+    if constexpr (EPI == EPI_GATE_RESID) {
+      if (lane == 0) bulk_wait_group0();  // every reduction of this warp has landed
     }
     if (PROBE && probe && warp == 2 && lane == 0) {
       probe[blockIdx.x * 8 + 4] = t_epi;
@@ -236,7 +254,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 }
 
 template <int EPI, bool OUT_F32, bool FP8 = false>
-int launch_pair_inst(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmArgs& g,
+int launch_pair_inst(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmR, const GemmArgs& g,
                      cudaStream_t stream) {
   auto kern = gemm_pair_tcgen05_kernel<EPI, OUT_F32, false, FP8>;
   auto kern_probe = gemm_pair_tcgen05_kernel<EPI, OUT_F32, !FP8, FP8>;  // no probe build of the e4m3 kernels
@@ -244,9 +262,9 @@ int launch_pair_inst(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmA
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_bytes(EPI));
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(kern_probe, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
+      e = cudaFuncSetAttribute(kern_probe, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_bytes(EPI));
     if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(gemm_pair)");
     attr_done[dev] = true;
   }
@@ -269,9 +287,9 @@ int launch_pair_inst(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmA
     if (probe) cudaMemset(probe, 0, sizeof(long long) * 8 * 2 * pairs);
   }
   if (probe)
-    kern_probe<<<2 * pairs, P_THREADS, P_SMEM_BYTES, stream>>>(tmA, tmW, g, probe, skip_loads);
+    kern_probe<<<2 * pairs, P_THREADS, pair_smem_bytes(EPI), stream>>>(tmA, tmW, tmR, g, probe, skip_loads);
   else
-    kern<<<2 * pairs, P_THREADS, P_SMEM_BYTES, stream>>>(tmA, tmW, g, nullptr, 0);
+    kern<<<2 * pairs, P_THREADS, pair_smem_bytes(EPI), stream>>>(tmA, tmW, tmR, g, nullptr, 0);
   const int rc = after_launch("gemm_pair_tcgen05_kernel");
   if (probe) {
     std::vector<long long> h(8 * 2 * pairs);
@@ -328,12 +346,21 @@ int launch_gemm_pair(const void* A, long lda, const void* W, long ldw, int opera
   rc = encode_tmap_2d(&tmW, W, eb, (uint64_t)K, (uint64_t)N, (uint64_t)ldw * eb, kel, P_BN_HALF);
   if (rc) return rc;
   const bool f32 = epi.out_f32 != 0;
+  CUtensorMap tmR = tmA;  // placeholder for the epilogues that do not reduce
+  if (epi.mode == EPI_GATE_RESID) {
+    if (epi.out != epi.resid) {
+      set_last_error("gemm_pair: gate/residual epilogue updates the residual in place (out must equal resid)");
+      return ST_INVALID_ARG;
+    }
+    rc = encode_tmap_2d(&tmR, epi.resid, 4, (uint64_t)N, (uint64_t)M, (uint64_t)epi.ldo * 4, 32, 32);
+    if (rc) return rc;
+  }
   if (fp8) {
     switch (epi.mode) {
-      case EPI_BIAS: return launch_pair_inst<EPI_BIAS, false, true>(tmA, tmW, g, stream);
-      case EPI_BIAS_GELU: return launch_pair_inst<EPI_BIAS_GELU, false, true>(tmA, tmW, g, stream);
-      case EPI_QKV_NORM: return launch_pair_inst<EPI_QKV_NORM, false, true>(tmA, tmW, g, stream);
-      case EPI_GATE_RESID: return launch_pair_inst<EPI_GATE_RESID, true, true>(tmA, tmW, g, stream);
+      case EPI_BIAS: return launch_pair_inst<EPI_BIAS, false, true>(tmA, tmW, tmR, g, stream);
+      case EPI_BIAS_GELU: return launch_pair_inst<EPI_BIAS_GELU, false, true>(tmA, tmW, tmR, g, stream);
+      case EPI_QKV_NORM: return launch_pair_inst<EPI_QKV_NORM, false, true>(tmA, tmW, tmR, g, stream);
+      case EPI_GATE_RESID: return launch_pair_inst<EPI_GATE_RESID, true, true>(tmA, tmW, tmR, g, stream);
       default: break;
     }
     set_last_error("gemm_pair: no e4m3 instantiation for epilogue mode %d", epi.mode);
@@ -341,20 +368,20 @@ int launch_gemm_pair(const void* A, long lda, const void* W, long ldw, int opera
   }
   switch (epi.mode) {
     case EPI_BIAS:
-      return f32 ? launch_pair_inst<EPI_BIAS, true>(tmA, tmW, g, stream)
-                 : launch_pair_inst<EPI_BIAS, false>(tmA, tmW, g, stream);
+      return f32 ? launch_pair_inst<EPI_BIAS, true>(tmA, tmW, tmR, g, stream)
+                 : launch_pair_inst<EPI_BIAS, false>(tmA, tmW, tmR, g, stream);
     case EPI_BIAS_GELU:
-      return f32 ? launch_pair_inst<EPI_BIAS_GELU, true>(tmA, tmW, g, stream)
-                 : launch_pair_inst<EPI_BIAS_GELU, false>(tmA, tmW, g, stream);
+      return f32 ? launch_pair_inst<EPI_BIAS_GELU, true>(tmA, tmW, tmR, g, stream)
+                 : launch_pair_inst<EPI_BIAS_GELU, false>(tmA, tmW, tmR, g, stream);
     case EPI_GATE_RESID:
       if (!f32) break;
-      return launch_pair_inst<EPI_GATE_RESID, true>(tmA, tmW, g, stream);
+      return launch_pair_inst<EPI_GATE_RESID, true>(tmA, tmW, tmR, g, stream);
     case EPI_QKV_NORM:
-      return f32 ? launch_pair_inst<EPI_QKV_NORM, true>(tmA, tmW, g, stream)
-                 : launch_pair_inst<EPI_QKV_NORM, false>(tmA, tmW, g, stream);
+      return f32 ? launch_pair_inst<EPI_QKV_NORM, true>(tmA, tmW, tmR, g, stream)
+                 : launch_pair_inst<EPI_QKV_NORM, false>(tmA, tmW, tmR, g, stream);
     case EPI_ADD_TABLE:
       if (!f32) break;
-      return launch_pair_inst<EPI_ADD_TABLE, true>(tmA, tmW, g, stream);
+      return launch_pair_inst<EPI_ADD_TABLE, true>(tmA, tmW, tmR, g, stream);
     default:
       break;
   }

@@ -315,5 +315,70 @@ __device__ __forceinline__ bool drain_tile(uint32_t t_row, int m, int n0, int ha
   return true;
 }
 
+
+// Gate + residual epilogue of the CTA-pair kernel through a TMA reduction:
+// resid += gate * (acc * alpha + bias) with the addition done at L2
+// (cp.reduce.async.bulk.tensor ... add.f32).  The SM neither reads the residual
+// nor stores it from registers: measured on the register path, those two made
+// the out-projection (K = 1536) 1.35x slower than its main loop.  A warp parks
+// 32 rows x 32 columns of increments in its 4 KiB of shared memory (128-byte
+// rows in the 128-byte swizzle the tensor map expects: 16-byte chunk c of row r
+// sits at chunk c ^ (r & 7), which also makes the row-per-thread writes
+// conflict-free) and lane 0 issues one reduction for the box.  Requires
+// out == resid.  `stage` is 1024-byte aligned.  m_w0: first row of this warp.
+template <int BN>
+__device__ __forceinline__ bool drain_tile_gate_reduce(uint32_t t_row, int m_w0, int n0, int half,
+                                                       const GemmArgs& g, const void* tmR,
+                                                       uint64_t* tfull_bar, uint32_t phase,
+                                                       const WaitCtx& wc, uint8_t* stage,
+                                                       long long* wait_clk = nullptr) {
+  constexpr int CPW = BN / 2, NSUB = CPW / 32;
+  const GemmEpilogue& e = g.epi;
+  const int lane = threadIdx.x & 31;
+  const int m = m_w0 + lane;
+  const int b = (m < g.M ? m : g.M - 1) / e.rows_in;
+  const float* gate_row = e.gate + static_cast<long>(b) * e.gate_stride;
+  const int nw = n0 + half * CPW;
+  float gg[32], bb[32];
+  load_f4_batch<8>(gate_row, nw, g.N, gg);
+  load_f4_batch<8>(e.bias, nw, g.N, bb);
+  const long long c0 = wait_clk ? clock64() : 0;
+  if (!mbar_wait_warp(tfull_bar, phase, wc, DEV_TIMEOUT_TMEM_FULL)) return false;
+  if (wait_clk) wait_clk[0] += clock64() - c0;
+  tc_fence_after_sync();
+  uint8_t* my_row = stage + lane * 128;
+#pragma unroll
+  for (int sub = 0; sub < NSUB; ++sub) {
+    const int n_base = nw + sub * 32;
+    uint32_t r[32];
+    tmem_ld_32x32b_x32(t_row + half * CPW + sub * 32, r);
+    tmem_wait_ld();
+    float d[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) d[j] = gg[j] * fmaf(__uint_as_float(r[j]), e.alpha, bb[j]);
+    if (sub + 1 < NSUB) {
+      load_f4_batch<8>(gate_row, n_base + 32, g.N, gg);
+      load_f4_batch<8>(e.bias, n_base + 32, g.N, bb);
+    }
+    // the previous reduction of this warp must have read the buffer
+    if (sub > 0 && lane == 0) bulk_wait_group_read0();
+    __syncwarp();
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+      *reinterpret_cast<float4*>(my_row + ((c ^ (lane & 7)) << 4)) =
+          make_float4(d[4 * c], d[4 * c + 1], d[4 * c + 2], d[4 * c + 3]);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0 && m_w0 < g.M) {
+      tma_reduce_add_2d(tmR, stage, n_base, m_w0);
+      bulk_commit_group();
+    }
+  }
+  // the buffer is reused by this warp's next tile
+  if (lane == 0) bulk_wait_group_read0();
+  __syncwarp();
+  return true;
+}
+
 }  // namespace gemm_detail
 }  // namespace sd3
