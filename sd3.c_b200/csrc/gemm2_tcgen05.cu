@@ -46,12 +46,17 @@ constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;  // 32 KiB
 // Stages of the operand ring: seven of 32 KiB, or six where the epilogue needs shared
 // memory of its own (gate + residual: 4 KiB per epilogue warp for the TMA reduction).
 constexpr int P_RED_BYTES = 4096;
-__host__ __device__ constexpr int pair_stages(int epi) { return epi == EPI_GATE_RESID ? 6 : 7; }
-__host__ __device__ constexpr int pair_red_bytes(int epi) { return epi == EPI_GATE_RESID ? EPI_WARPS * P_RED_BYTES : 0; }
+__host__ __device__ constexpr bool pair_stages_out(int epi, bool out_f32) {
+  return epi == EPI_GATE_RESID || (!out_f32 && (epi == EPI_BIAS || epi == EPI_BIAS_GELU || epi == EPI_QKV_NORM));
+}
+__host__ __device__ constexpr int pair_stages(int epi, bool out_f32) { return pair_stages_out(epi, out_f32) ? 6 : 7; }
+__host__ __device__ constexpr int pair_red_bytes(int epi, bool out_f32) {
+  return pair_stages_out(epi, out_f32) ? EPI_WARPS * P_RED_BYTES : 0;
+}
 constexpr int P_TMEM_COLS = 512;     // two accumulators of 256 columns
 constexpr int P_THREADS = 64 + 32 * EPI_WARPS;
-__host__ __device__ constexpr int pair_smem_bytes(int epi) {
-  return pair_stages(epi) * P_STAGE_BYTES + pair_red_bytes(epi) + 256 + 1024;
+__host__ __device__ constexpr int pair_smem_bytes(int epi, bool out_f32) {
+  return pair_stages(epi, out_f32) * P_STAGE_BYTES + pair_red_bytes(epi, out_f32) + 256 + 1024;
 }
 
 // PROBE: cycle counters compiled in (diagnostic instantiation only; even behind a
@@ -69,9 +74,9 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  constexpr int P_STAGES = pair_stages(EPI);
+  constexpr int P_STAGES = pair_stages(EPI, OUT_F32);
   uint8_t* red_smem = smem + P_STAGES * P_STAGE_BYTES;  // 1024-byte aligned: stages are 32 KiB each
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + P_STAGES * P_STAGE_BYTES + pair_red_bytes(EPI));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + P_STAGES * P_STAGE_BYTES + pair_red_bytes(EPI, OUT_F32));
   uint64_t* empty_bar = full_bar + P_STAGES;
   uint64_t* tfull_bar = empty_bar + P_STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
@@ -221,8 +226,9 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                                                acc_phase, wc, red_smem + (warp - 2) * P_RED_BYTES,
                                                (PROBE && probe) ? w_epi : nullptr);
       else
-        drained = drain_tile<P_BN, EPI, OUT_F32>(t_row, m0 + row, n0, half, g, &tfull_bar[acc], acc_phase, wc,
-                                                 (PROBE && probe) ? w_epi : nullptr);
+        drained = drain_tile<P_BN, EPI, OUT_F32>(
+            t_row, m0 + row, n0, half, g, &tfull_bar[acc], acc_phase, wc, (PROBE && probe) ? w_epi : nullptr,
+            (pair_stages_out(EPI, OUT_F32) && g.tma_store) ? red_smem + (warp - 2) * P_RED_BYTES : nullptr, &tmR);
       if (!drained) break;
       if (PROBE && probe) t_epi += clock64() - c0;  // includes the wait for the accumulator
       tc_fence_before_sync();
@@ -231,8 +237,8 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
-    if constexpr (EPI == EPI_GATE_RESID) {
-      if (lane == 0) bulk_wait_group0();  // every reduction of this warp has landed
+    if constexpr (pair_stages_out(EPI, OUT_F32)) {
+      if (lane == 0) bulk_wait_group0();  // every reduction / store of this warp has landed
     }
     if (PROBE && probe && warp == 2 && lane == 0) {
       probe[blockIdx.x * 8 + 4] = t_epi;
@@ -262,9 +268,9 @@ int launch_pair_inst(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUten
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_bytes(EPI));
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_bytes(EPI, OUT_F32));
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(kern_probe, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_bytes(EPI));
+      e = cudaFuncSetAttribute(kern_probe, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_bytes(EPI, OUT_F32));
     if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(gemm_pair)");
     attr_done[dev] = true;
   }
@@ -287,9 +293,9 @@ int launch_pair_inst(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUten
     if (probe) cudaMemset(probe, 0, sizeof(long long) * 8 * 2 * pairs);
   }
   if (probe)
-    kern_probe<<<2 * pairs, P_THREADS, pair_smem_bytes(EPI), stream>>>(tmA, tmW, tmR, g, probe, skip_loads);
+    kern_probe<<<2 * pairs, P_THREADS, pair_smem_bytes(EPI, OUT_F32), stream>>>(tmA, tmW, tmR, g, probe, skip_loads);
   else
-    kern<<<2 * pairs, P_THREADS, pair_smem_bytes(EPI), stream>>>(tmA, tmW, tmR, g, nullptr, 0);
+    kern<<<2 * pairs, P_THREADS, pair_smem_bytes(EPI, OUT_F32), stream>>>(tmA, tmW, tmR, g, nullptr, 0);
   const int rc = after_launch("gemm_pair_tcgen05_kernel");
   if (probe) {
     std::vector<long long> h(8 * 2 * pairs);
@@ -354,6 +360,22 @@ int launch_gemm_pair(const void* A, long lda, const void* W, long ldw, int opera
     }
     rc = encode_tmap_2d(&tmR, epi.resid, 4, (uint64_t)N, (uint64_t)M, (uint64_t)epi.ldo * 4, 32, 32);
     if (rc) return rc;
+  }
+  // bf16 outputs leave through a TMA store when every warp's 32 rows are 32 consecutive
+  // output rows that all exist
+  g.tma_store = 0;
+  if (!f32 && !epi.out_e4m3 && M % 32 == 0 && (epi.rows_in == 0 || epi.rows_in % 32 == 0) &&
+      (epi.mode == EPI_BIAS || epi.mode == EPI_BIAS_GELU || epi.mode == EPI_QKV_NORM) &&
+      (epi.ldo * 2) % 16 == 0 && (reinterpret_cast<uintptr_t>(epi.out) & 15) == 0) {
+    const uint64_t out_rows =
+        epi.rows_in > 0 ? (uint64_t)(M / epi.rows_in) * epi.rows_out + 0 : (uint64_t)M;
+    // with a row remap the last sample's rows end at (samples - 1) * rows_out + row_off + rows_in
+    const uint64_t extent = epi.rows_in > 0
+                                ? (uint64_t)(M / epi.rows_in - 1) * epi.rows_out + epi.row_off + epi.rows_in
+                                : out_rows;
+    rc = encode_tmap_2d(&tmR, epi.out, 2, (uint64_t)N, extent, (uint64_t)epi.ldo * 2, 64, 32);
+    if (rc) return rc;
+    g.tma_store = 1;
   }
   if (fp8) {
     switch (epi.mode) {

@@ -23,6 +23,7 @@ struct GemmArgs {
   int tiles_m, tiles_n;
   GemmEpilogue epi;
   int wide_store;    // output rows are 32-byte aligned at every 16-column (bf16) / 8-column (f32) group
+  int tma_store;     // CTA-pair kernel: bf16 output leaves through shared memory and a TMA store
   int* status;
 };
 
@@ -134,9 +135,14 @@ __device__ __forceinline__ RowMap map_row(int m, const GemmEpilogue& e) {
 
 // Epilogue for 64 consecutive accumulator columns of one row; v already holds
 // acc * alpha + bias.
+// stage / tmO (both or neither): 4 KiB of 1024-byte aligned shared memory private to the
+// warp and the tensor map of the bf16 output.  With them the warp's 32 rows x 64 columns
+// leave as ONE TMA store (rows in the 128-byte swizzle, 16-byte chunk c of row r at chunk
+// c ^ (r & 7)) instead of 128 32-byte register stores; orow0 is the output row of lane 0.
 template <int EPI, bool OUT_F32>
 __device__ __forceinline__ void epilogue_64(float (&v)[64], const RowMap& rm, int n_base,
-                                            const GemmArgs& g) {
+                                            const GemmArgs& g, uint8_t* stage = nullptr,
+                                            const void* tmO = nullptr, long orow0 = 0) {
   const GemmEpilogue& e = g.epi;
   const int N = g.N;
   if constexpr (EPI == EPI_QKV_NORM) {
@@ -191,6 +197,26 @@ __device__ __forceinline__ void epilogue_64(float (&v)[64], const RowMap& rm, in
 #pragma unroll
     for (int j = 0; j < 64; ++j) v[j] += tt[j];
   }
+  if constexpr (!OUT_F32 && (EPI == EPI_BIAS || EPI == EPI_BIAS_GELU || EPI == EPI_QKV_NORM)) {
+    if (stage != nullptr && !e.out_e4m3) {  // warp-uniform
+      const int lane = threadIdx.x & 31;
+      if (lane == 0) bulk_wait_group_read0();  // the previous store of this warp has read the buffer
+      __syncwarp();
+      uint8_t* my_row = stage + lane * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<uint4*>(my_row + ((c ^ (lane & 7)) << 4)) =
+            make_uint4(pack_bf16x2(v[8 * c], v[8 * c + 1]), pack_bf16x2(v[8 * c + 2], v[8 * c + 3]),
+                       pack_bf16x2(v[8 * c + 4], v[8 * c + 5]), pack_bf16x2(v[8 * c + 6], v[8 * c + 7]));
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(tmO, stage, n_base, static_cast<int>(orow0));
+        bulk_commit_group();
+      }
+      return;
+    }
+  }
   const long base = rm.orow * e.ldo;
   if constexpr (!OUT_F32 && (EPI == EPI_BIAS || EPI == EPI_BIAS_GELU)) {
     if (e.out_e4m3) {  // 64 bytes per thread; N % 64 == 0 is checked at launch
@@ -227,7 +253,8 @@ __device__ __forceinline__ void epilogue_64(float (&v)[64], const RowMap& rm, in
 template <int BN, int EPI, bool OUT_F32>
 __device__ __forceinline__ bool drain_tile(uint32_t t_row, int m, int n0, int half, const GemmArgs& g,
                                            uint64_t* tfull_bar, uint32_t phase, const WaitCtx& wc,
-                                           long long* wait_clk = nullptr) {
+                                           long long* wait_clk = nullptr, uint8_t* stage = nullptr,
+                                           const void* tmO = nullptr) {
   constexpr int COLS_PER_WARP = BN / 2;
   const GemmEpilogue& e = g.epi;
   const bool valid = m < g.M;
@@ -304,7 +331,12 @@ __device__ __forceinline__ bool drain_tile(uint32_t t_row, int m, int n0, int ha
         v[j] = fmaf(__uint_as_float(r0[j]), e.alpha, bb[j]);
         v[32 + j] = fmaf(__uint_as_float(r1[j]), e.alpha, bb[32 + j]);
       }
-      if (valid) epilogue_64<EPI, OUT_F32>(v, rm, n_base, g);
+      if (stage != nullptr) {
+        // whole warp valid or not at all (M % 32 == 0 is a condition of this path)
+        if (valid) epilogue_64<EPI, OUT_F32>(v, rm, n_base, g, stage, tmO, rm.orow - (threadIdx.x & 31));
+      } else if (valid) {
+        epilogue_64<EPI, OUT_F32>(v, rm, n_base, g);
+      }
       if (ci + 1 < CHUNKS) load_f4_batch<16>(e.bias, n_base + 64, g.N, bb);  // next chunk's bias
       if (wait_clk) {
         wait_clk[1] += c2 - c1;

@@ -401,6 +401,7 @@ int launch_gemm(const void* A, long lda, const void* W, long ldw, int operand_dt
                    ((reinterpret_cast<uintptr_t>(epi.out) & 31) == 0);
   }
 
+  g.tma_store = 0;  // register stores in the one-CTA kernel
   CUtensorMap tmA, tmW;
   int rc = encode_tmap_2d(&tmA, A, eb, (uint64_t)K, (uint64_t)M, (uint64_t)lda * eb,
                           elems_per_stage, BM);

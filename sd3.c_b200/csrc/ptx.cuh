@@ -176,6 +176,13 @@ __device__ __forceinline__ void tma_reduce_add_2d(const void* tmap, const void* 
       ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
       : "memory");
 }
+// TMA store: global[tile] = shared[tile] (same rules as the reduction above)
+__device__ __forceinline__ void tma_store_2d(const void* tmap, const void* smem_src, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+      : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // until the bulk operations of this thread have finished READING their shared-memory source
 __device__ __forceinline__ void bulk_wait_group_read0() {
