@@ -49,7 +49,10 @@ constexpr int P_RED_BYTES = 4096;
 __host__ __device__ constexpr bool pair_stages_out(int epi, bool out_f32) {
   return epi == EPI_GATE_RESID || (!out_f32 && (epi == EPI_BIAS || epi == EPI_BIAS_GELU || epi == EPI_QKV_NORM));
 }
-__host__ __device__ constexpr int pair_stages(int epi, bool out_f32) { return pair_stages_out(epi, out_f32) ? 6 : 7; }
+// Six stages everywhere: they are handed over in SLOTS of two (one full/empty barrier pair,
+// one barrier test and one tcgen05.commit per 64 KiB instead of per 32 KiB: the issuing
+// thread spent ~100 of every 680 cycles of a stage on those two).
+__host__ __device__ constexpr int pair_stages(int, bool) { return 6; }
 __host__ __device__ constexpr int pair_red_bytes(int epi, bool out_f32) {
   return pair_stages_out(epi, out_f32) ? EPI_WARPS * P_RED_BYTES : 0;
 }
@@ -116,6 +119,8 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 
   const int num_tiles = g.tiles_m * g.tiles_n;  // tiles of 256 x 256
   const int KB = g.k_blocks;
+  constexpr int NSLOT = P_STAGES / 2;  // slots of two stages
+  const int KS = (KB + 1) / 2;         // slots per tile (the last may hold one stage)
 
   if (warp == 0 && lane == 0) {
     // ------------------------------ TMA producer (both CTAs, one thread) ------
@@ -126,24 +131,27 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
       const int m0 = (tile / g.tiles_n) * (2 * P_BM) + static_cast<int>(rank) * P_BM;
       const int n0 = (tile % g.tiles_n) * P_BN + static_cast<int>(rank) * P_BN_HALF;
-      for (int kb = 0; kb < KB; ++kb) {
+      for (int ks = 0; ks < KS; ++ks) {
         const long long c0 = (PROBE && probe) ? clock64() : 0;
         if (!mbar_wait(&empty_bar[stage], phase ^ 1, wc, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
         if (PROBE && probe) w_empty += clock64() - c0;
         {
-          uint8_t* sa = smem + stage * P_STAGE_BYTES;
-          // all bytes of the stage (both CTAs) are credited to the leader's barrier
+          const int nk = KB - 2 * ks < 2 ? KB - 2 * ks : 2;  // stages of this slot that carry data
+          // all bytes of the slot (both CTAs) are credited to the leader's barrier
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
-          if (PROBE && skip_loads && (tile != pair || kb >= P_STAGES)) {
+          if (PROBE && skip_loads && (tile != pair || ks >= NSLOT)) {
             if (rank == 0) mbar_arrive(&full_bar[stage]);  // experiment: reuse stale operands
           } else {
-            if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * P_STAGE_BYTES);
+            if (rank == 0) mbar_expect_tx(&full_bar[stage], nk * 2 * P_STAGE_BYTES);
             constexpr int KEL = FP8 ? P_KBYTES : P_KBYTES / 2;  // K elements per stage
-            tma_load_2d_pair(sa, &tmA, bar, kb * KEL, m0);
-            tma_load_2d_pair(sa + P_A_BYTES, &tmW, bar, kb * KEL, n0);
+            for (int hs = 0; hs < nk; ++hs) {
+              uint8_t* sa = smem + (2 * stage + hs) * P_STAGE_BYTES;
+              tma_load_2d_pair(sa, &tmA, bar, (2 * ks + hs) * KEL, m0);
+              tma_load_2d_pair(sa + P_A_BYTES, &tmW, bar, (2 * ks + hs) * KEL, n0);
+            }
           }
         }
-        if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        if (++stage == NSLOT) { stage = 0; phase ^= 1; }
       }
     }
     if (PROBE && probe) probe[blockIdx.x * 8 + 0] = w_empty;
@@ -164,8 +172,8 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         if (PROBE && probe) w_tempty += clock64() - c0;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * P_BN);
-        for (int kb = 0; kb < KB; ++kb) {
-          // The readiness of this stage was tested while the previous stage's
+        for (int ks = 0; ks < KS; ++ks) {
+          // The readiness of this slot was tested while the previous slot's
           // MMAs were being issued; only fall back to a blocking wait if that
           // early test failed.
           if (!stage_ready) {
@@ -175,24 +183,25 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           }
           int ns = stage + 1;
           uint32_t np = phase;
-          if (ns == P_STAGES) { ns = 0; np ^= 1; }
+          if (ns == NSLOT) { ns = 0; np ^= 1; }
           const uint32_t next_ready = mbar_test_wait(&full_bar[ns], np);  // result consumed after the MMAs
           tc_fence_after_sync();
-          {
-            const uint32_t a_addr = smem_u32(smem + stage * P_STAGE_BYTES);
+          const int nk = KB - 2 * ks < 2 ? KB - 2 * ks : 2;
+          for (int hs = 0; hs < nk; ++hs) {
+            const uint32_t a_addr = smem_u32(smem + (2 * stage + hs) * P_STAGE_BYTES);
             const uint64_t a_desc = make_smem_desc_sw128(a_addr, 16, 1024);
             const uint64_t b_desc = make_smem_desc_sw128(a_addr + P_A_BYTES, 16, 1024);
 #pragma unroll
             for (int k = 0; k < P_KBYTES / 32; ++k) {
               const uint64_t adv = static_cast<uint64_t>((k * 32) >> 4);
               if constexpr (FP8)
-                mma_f8_ss_pair(d_tmem, a_desc + adv, b_desc + adv, IDESC, (kb | k) != 0);
+                mma_f8_ss_pair(d_tmem, a_desc + adv, b_desc + adv, IDESC, (ks | hs | k) != 0);
               else
-                mma_f16_ss_pair(d_tmem, a_desc + adv, b_desc + adv, IDESC, (kb | k) != 0);
+                mma_f16_ss_pair(d_tmem, a_desc + adv, b_desc + adv, IDESC, (ks | hs | k) != 0);
             }
-            mma_commit_pair(&empty_bar[stage], 3);          // frees the stage in both CTAs
-            if (kb == KB - 1) mma_commit_pair(&tfull_bar[acc], 3);  // accumulator ready in both CTAs
           }
+          mma_commit_pair(&empty_bar[stage], 3);          // frees the slot in both CTAs
+          if (ks == KS - 1) mma_commit_pair(&tfull_bar[acc], 3);  // accumulator ready in both CTAs
           stage = ns;
           phase = np;
           stage_ready = next_ready != 0;
