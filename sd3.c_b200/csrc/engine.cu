@@ -39,6 +39,7 @@ struct Linear {
   // FP8 mode: the same matrix as e4m3 = round(w / wscale), wscale = max|w| / 448
   void* w8 = nullptr;
   float wscale = 1.0f;
+  bool w8_stale = false;  // w was rewritten after w8 was formed: requantise at the next finalize
 };
 
 struct LayerW {
@@ -90,6 +91,7 @@ struct sd3_model {
   float* pos_store = nullptr;
   size_t pos_store_elems = 0;
   int* status = nullptr;
+  float* amax_scratch = nullptr;  // one float for the weight quantiser
   bool finalized = false;
 
   size_t wbytes() const { return f32 ? 4 : 2; }
@@ -441,16 +443,18 @@ int block_body(sd3_model* m, int l, float* c, float* x, int B, int Tc, int Tx, c
 
 // FP8 mode: every block GEMM weight gets an e4m3 twin with one scale per matrix.
 int quantize_block_weights(sd3_model* m) {
-  float* d_amax = nullptr;
   int rc = check_cuda(cudaDeviceSynchronize(), "parameter copies");  // whatever stream packed them
   if (rc) return rc;
-  rc = dev_alloc(m, reinterpret_cast<void**>(&d_amax), 4);
-  if (rc) return rc;
+  if (!m->amax_scratch) {
+    rc = dev_alloc(m, reinterpret_cast<void**>(&m->amax_scratch), 4);
+    if (rc) return rc;
+  }
+  float* d_amax = m->amax_scratch;
   for (LayerW& Lw : m->layers) {
     Linear* all[] = {&Lw.c_qkv, &Lw.c_out, &Lw.c_mlp1, &Lw.c_mlp2, &Lw.x_qkv,
                      &Lw.x_out, &Lw.x_mlp1, &Lw.x_mlp2, &Lw.d_qkv, &Lw.d_out};
     for (Linear* L : all) {
-      if (!L->w || L->w8) continue;
+      if (!L->w || (L->w8 && !L->w8_stale)) continue;
       const long n = static_cast<long>(L->N) * L->K;
       if (n % 4 || L->K % 16) continue;  // stays bf16
       rc = launch_absmax(L->w, 0, n, d_amax, nullptr);
@@ -460,10 +464,13 @@ int quantize_block_weights(sd3_model* m) {
       if (rc) return rc;
       if (!(amax > 0.f)) amax = 1.0f;
       L->wscale = amax / 448.0f;
-      rc = dev_alloc(m, &L->w8, static_cast<size_t>(n));
-      if (rc) return rc;
+      if (!L->w8) {  // a rewritten weight keeps its e4m3 buffer (same shape)
+        rc = dev_alloc(m, &L->w8, static_cast<size_t>(n));
+        if (rc) return rc;
+      }
       rc = launch_quantize_e4m3(L->w, 0, L->w8, n, 1.0f / L->wscale, nullptr);
       if (rc) return rc;
+      L->w8_stale = false;
     }
   }
   return check_cuda(cudaDeviceSynchronize(), "quantize weights");
@@ -598,6 +605,7 @@ int sd3_model_set_param(sd3_model* m, const char* name, const void* dev_ptr, int
       dst = s.lin->w;
       s.lin->N = s.N;
       s.lin->K = s.K;
+      if (s.lin->w8) s.lin->w8_stale = true;
     }
     if (!rc) {
       if (s.conv) {

@@ -17,10 +17,7 @@
 // Loads are plain tiled TMA (cta_group::2 form so the peer's transaction bytes
 // can be credited to the leader's barrier); nothing here is a multicast load.
 #include <cuda.h>
-#include <stdio.h>
-#include <stdlib.h>
-
-#include <vector>
+#include <mutex>
 
 #include "gemm_epilogue.cuh"
 #include "kernels.h"
@@ -62,14 +59,12 @@ __host__ __device__ constexpr int pair_smem_bytes(int epi, bool out_f32) {
   return pair_stages(epi, out_f32) * P_STAGE_BYTES + pair_red_bytes(epi, out_f32) + 256 + 1024;
 }
 
-// PROBE: cycle counters compiled in (diagnostic instantiation only; even behind a
-// runtime flag they slow the issue loops down).
-template <int EPI, bool OUT_F32, bool PROBE, bool FP8>
+template <int EPI, bool OUT_F32, bool FP8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                          const __grid_constant__ CUtensorMap tmW,
                          const __grid_constant__ CUtensorMap tmR,  // fp32 residual, gate + residual epilogue only
-                         const GemmArgs g, long long* __restrict__ probe, int skip_loads) {
+                         const GemmArgs g) {
   // M = 256 across the pair; operands bf16, or e4m3 (128 K-elements per 128-byte stage row,
   // 32 per instruction: the byte arithmetic of the stages is the same)
   constexpr uint32_t IDESC = FP8 ? make_idesc(0, 0, 2 * P_BM, P_BN, 0, 0) : make_idesc(1, 1, 2 * P_BM, P_BN, 0, 0);
@@ -127,34 +122,26 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    long long w_empty = 0;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
       const int m0 = (tile / g.tiles_n) * (2 * P_BM) + static_cast<int>(rank) * P_BM;
       const int n0 = (tile % g.tiles_n) * P_BN + static_cast<int>(rank) * P_BN_HALF;
       for (int ks = 0; ks < KS; ++ks) {
-        const long long c0 = (PROBE && probe) ? clock64() : 0;
         if (!mbar_wait(&empty_bar[stage], phase ^ 1, wc, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
-        if (PROBE && probe) w_empty += clock64() - c0;
         {
           const int nk = KB - 2 * ks < 2 ? KB - 2 * ks : 2;  // stages of this slot that carry data
           // all bytes of the slot (both CTAs) are credited to the leader's barrier
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
-          if (PROBE && skip_loads && (tile != pair || ks >= NSLOT)) {
-            if (rank == 0) mbar_arrive(&full_bar[stage]);  // experiment: reuse stale operands
-          } else {
-            if (rank == 0) mbar_expect_tx(&full_bar[stage], nk * 2 * P_STAGE_BYTES);
-            constexpr int KEL = FP8 ? P_KBYTES : P_KBYTES / 2;  // K elements per stage
-            for (int hs = 0; hs < nk; ++hs) {
-              uint8_t* sa = smem + (2 * stage + hs) * P_STAGE_BYTES;
-              tma_load_2d_pair(sa, &tmA, bar, (2 * ks + hs) * KEL, m0);
-              tma_load_2d_pair(sa + P_A_BYTES, &tmW, bar, (2 * ks + hs) * KEL, n0);
-            }
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], nk * 2 * P_STAGE_BYTES);
+          constexpr int KEL = FP8 ? P_KBYTES : P_KBYTES / 2;  // K elements per stage
+          for (int hs = 0; hs < nk; ++hs) {
+            uint8_t* sa = smem + (2 * stage + hs) * P_STAGE_BYTES;
+            tma_load_2d_pair(sa, &tmA, bar, (2 * ks + hs) * KEL, m0);
+            tma_load_2d_pair(sa + P_A_BYTES, &tmW, bar, (2 * ks + hs) * KEL, n0);
           }
         }
         if (++stage == NSLOT) { stage = 0; phase ^= 1; }
       }
     }
-    if (PROBE && probe) probe[blockIdx.x * 8 + 0] = w_empty;
   } else if (warp == 1 && lane == 0) {
     // ------------------------------ MMA issuer (leader only) ------------------
     if (rank == 0) {
@@ -163,13 +150,9 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      long long w_full = 0, w_tempty = 0;
       bool stage_ready = false;
-      const long long t_begin = (PROBE && probe) ? clock64() : 0;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        const long long c0 = (PROBE && probe) ? clock64() : 0;
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, wc, DEV_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
-        if (PROBE && probe) w_tempty += clock64() - c0;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * P_BN);
         for (int ks = 0; ks < KS; ++ks) {
@@ -177,9 +160,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           // MMAs were being issued; only fall back to a blocking wait if that
           // early test failed.
           if (!stage_ready) {
-            const long long c1 = (PROBE && probe) ? clock64() : 0;
             if (!mbar_wait(&full_bar[stage], phase, wc, DEV_TIMEOUT_FULL)) { ok = false; break; }
-            if (PROBE && probe) w_full += clock64() - c1;
           }
           int ns = stage + 1;
           uint32_t np = phase;
@@ -209,11 +190,6 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
-      if (PROBE && probe) {
-        probe[blockIdx.x * 8 + 1] = w_full;
-        probe[blockIdx.x * 8 + 2] = w_tempty;
-        probe[blockIdx.x * 8 + 3] = clock64() - t_begin;
-      }
     }
   } else if (warp >= 2) {
     // ------------------------------ epilogue (both CTAs) ----------------------
@@ -222,24 +198,20 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     const int row = quad * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
-    long long t_epi = 0, w_epi[3] = {0, 0, 0};
     for (int tile = pair; tile < num_tiles; tile += num_pairs) {
       const int m0 = (tile / g.tiles_n) * (2 * P_BM) + static_cast<int>(rank) * P_BM;
       const int n0 = (tile % g.tiles_n) * P_BN;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                              static_cast<uint32_t>(acc * P_BN);
-      const long long c0 = (PROBE && probe) ? clock64() : 0;
       bool drained;
       if constexpr (EPI == EPI_GATE_RESID)
         drained = drain_tile_gate_reduce<P_BN>(t_row, m0 + quad * 32, n0, half, g, &tmR, &tfull_bar[acc],
-                                               acc_phase, wc, red_smem + (warp - 2) * P_RED_BYTES,
-                                               (PROBE && probe) ? w_epi : nullptr);
+                                               acc_phase, wc, red_smem + (warp - 2) * P_RED_BYTES);
       else
         drained = drain_tile<P_BN, EPI, OUT_F32>(
-            t_row, m0 + row, n0, half, g, &tfull_bar[acc], acc_phase, wc, (PROBE && probe) ? w_epi : nullptr,
+            t_row, m0 + row, n0, half, g, &tfull_bar[acc], acc_phase, wc,
             (pair_stages_out(EPI, OUT_F32) && g.tma_store) ? red_smem + (warp - 2) * P_RED_BYTES : nullptr, &tmR);
       if (!drained) break;
-      if (PROBE && probe) t_epi += clock64() - c0;  // includes the wait for the accumulator
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
@@ -248,12 +220,6 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     }
     if constexpr (pair_stages_out(EPI, OUT_F32)) {
       if (lane == 0) bulk_wait_group0();  // every reduction / store of this warp has landed
-    }
-    if (PROBE && probe && warp == 2 && lane == 0) {
-      probe[blockIdx.x * 8 + 4] = t_epi;
-      probe[blockIdx.x * 8 + 5] = w_epi[0];
-      probe[blockIdx.x * 8 + 6] = w_epi[1];
-      probe[blockIdx.x * 8 + 7] = w_epi[2];
     }
   }
 
@@ -271,56 +237,24 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 template <int EPI, bool OUT_F32, bool FP8 = false>
 int launch_pair_inst(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmR, const GemmArgs& g,
                      cudaStream_t stream) {
-  auto kern = gemm_pair_tcgen05_kernel<EPI, OUT_F32, false, FP8>;
-  auto kern_probe = gemm_pair_tcgen05_kernel<EPI, OUT_F32, !FP8, FP8>;  // no probe build of the e4m3 kernels
+  auto kern = gemm_pair_tcgen05_kernel<EPI, OUT_F32, FP8>;
+  static std::mutex attr_mutex;
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_bytes(EPI, OUT_F32));
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(kern_probe, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_bytes(EPI, OUT_F32));
-    if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(gemm_pair)");
-    attr_done[dev] = true;
+  if (dev >= 0 && dev < 64) {
+    std::lock_guard<std::mutex> lock(attr_mutex);
+    if (!attr_done[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_bytes(EPI, OUT_F32));
+      if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(gemm_pair)");
+      attr_done[dev] = true;
+    }
   }
   const int tiles = g.tiles_m * g.tiles_n;
   const int max_pairs = device_sm_count() / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
-  // Diagnostic: SD3_GEMM_PROBE=1 makes every launch synchronous and prints where
-  // the roles of the kernel spent their cycles (averages over CTAs).
-  static const bool probing = []() {
-    const char* v = getenv("SD3_GEMM_PROBE");
-    return v && (v[0] == '1' || v[0] == '2');
-  }();
-  static const int skip_loads = []() {
-    const char* v = getenv("SD3_GEMM_PROBE");
-    return (v && v[0] == '2') ? 1 : 0;
-  }();
-  long long* probe = nullptr;
-  if (probing && !FP8 && g.status) {  // never on the allocation-free entry point (no status word there)
-    if (cudaMalloc(&probe, sizeof(long long) * 8 * 2 * pairs) != cudaSuccess) probe = nullptr;
-    if (probe) cudaMemset(probe, 0, sizeof(long long) * 8 * 2 * pairs);
-  }
-  if (probe)
-    kern_probe<<<2 * pairs, P_THREADS, pair_smem_bytes(EPI, OUT_F32), stream>>>(tmA, tmW, tmR, g, probe, skip_loads);
-  else
-    kern<<<2 * pairs, P_THREADS, pair_smem_bytes(EPI, OUT_F32), stream>>>(tmA, tmW, tmR, g, nullptr, 0);
-  const int rc = after_launch("gemm_pair_tcgen05_kernel");
-  if (probe) {
-    std::vector<long long> h(8 * 2 * pairs);
-    cudaStreamSynchronize(stream);
-    cudaMemcpy(h.data(), probe, h.size() * sizeof(long long), cudaMemcpyDeviceToHost);
-    cudaFree(probe);
-    double s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int c = 0; c < 2 * pairs; ++c)
-      for (int i = 0; i < 8; ++i) s[i] += static_cast<double>(h[c * 8 + i]);
-    fprintf(stderr,
-            "[gemm_pair probe] M %d N %d K %d epi %d: mma loop %.0f clk/CTA (wait operands %.0f, wait "
-            "epilogue %.0f), producer wait-empty %.0f, epilogue warp total %.0f: waiting %.0f, TMEM loads %.0f, math+stores %.0f\n",
-            g.M, g.N, g.K, g.epi.mode, s[3] / pairs, s[1] / pairs, s[2] / pairs, s[0] / (2 * pairs),
-            s[4] / (2 * pairs), s[5] / (2 * pairs), s[6] / (2 * pairs), s[7] / (2 * pairs));
-  }
-  return rc;
+  kern<<<2 * pairs, P_THREADS, pair_smem_bytes(EPI, OUT_F32), stream>>>(tmA, tmW, tmR, g);
+  return after_launch("gemm_pair_tcgen05_kernel");
 }
 
 }  // namespace

@@ -248,13 +248,10 @@ __device__ __forceinline__ void epilogue_64(float (&v)[64], const RowMap& rm, in
 // t_row: TMEM address of the accumulator (lane quadrant and column base applied);
 // m: global output row of this thread; n0: first output column of the tile.
 // Waits for the accumulator on tfull_bar; returns false if that wait gave up.
-// wait_clk (optional, diagnostics): [0] cycles waiting for the accumulator,
-// [1] TMEM loads, [2] math and stores.
 template <int BN, int EPI, bool OUT_F32>
 __device__ __forceinline__ bool drain_tile(uint32_t t_row, int m, int n0, int half, const GemmArgs& g,
                                            uint64_t* tfull_bar, uint32_t phase, const WaitCtx& wc,
-                                           long long* wait_clk = nullptr, uint8_t* stage = nullptr,
-                                           const void* tmO = nullptr) {
+                                           uint8_t* stage = nullptr, const void* tmO = nullptr) {
   constexpr int COLS_PER_WARP = BN / 2;
   const GemmEpilogue& e = g.epi;
   const bool valid = m < g.M;
@@ -274,9 +271,7 @@ __device__ __forceinline__ bool drain_tile(uint32_t t_row, int m, int n0, int ha
       load_f4_batch<8>(gate_row, nw, g.N, gg);
       load_f4_batch<8>(e.bias, nw, g.N, bb);
     }
-    const long long c0 = wait_clk ? clock64() : 0;
     if (!mbar_wait_warp(tfull_bar, phase, wc, DEV_TIMEOUT_TMEM_FULL)) return false;
-    if (wait_clk) wait_clk[0] += clock64() - c0;
     tc_fence_after_sync();
 #pragma unroll
     for (int sub = 0; sub < NSUB; ++sub) {
@@ -310,9 +305,7 @@ __device__ __forceinline__ bool drain_tile(uint32_t t_row, int m, int n0, int ha
     const int c_first = COLS_PER_WARP >= 64 ? half * CHUNKS : 0;
     float bb[64];
     if (active) load_f4_batch<16>(e.bias, n0 + c_first * 64, g.N, bb);
-    const long long c0 = wait_clk ? clock64() : 0;
     if (!mbar_wait_warp(tfull_bar, phase, wc, DEV_TIMEOUT_TMEM_FULL)) return false;
-    if (wait_clk) wait_clk[0] += clock64() - c0;
     tc_fence_after_sync();
 #pragma unroll 1
     for (int ci = 0; ci < CHUNKS; ++ci) {
@@ -320,11 +313,9 @@ __device__ __forceinline__ bool drain_tile(uint32_t t_row, int m, int n0, int ha
       const int n_base = n0 + c * 64;
       if (!active || n_base >= g.N) break;  // warp-uniform
       uint32_t r0[32], r1[32];
-      const long long c1 = wait_clk ? clock64() : 0;
       tmem_ld_32x32b_x32(t_row + c * 64, r0);
       tmem_ld_32x32b_x32(t_row + c * 64 + 32, r1);
       tmem_wait_ld();
-      const long long c2 = wait_clk ? clock64() : 0;
       float v[64];
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
@@ -338,10 +329,6 @@ __device__ __forceinline__ bool drain_tile(uint32_t t_row, int m, int n0, int ha
         epilogue_64<EPI, OUT_F32>(v, rm, n_base, g);
       }
       if (ci + 1 < CHUNKS) load_f4_batch<16>(e.bias, n_base + 64, g.N, bb);  // next chunk's bias
-      if (wait_clk) {
-        wait_clk[1] += c2 - c1;
-        wait_clk[2] += clock64() - c2;
-      }
     }
   }
   return true;
@@ -362,8 +349,7 @@ template <int BN>
 __device__ __forceinline__ bool drain_tile_gate_reduce(uint32_t t_row, int m_w0, int n0, int half,
                                                        const GemmArgs& g, const void* tmR,
                                                        uint64_t* tfull_bar, uint32_t phase,
-                                                       const WaitCtx& wc, uint8_t* stage,
-                                                       long long* wait_clk = nullptr) {
+                                                       const WaitCtx& wc, uint8_t* stage) {
   constexpr int CPW = BN / 2, NSUB = CPW / 32;
   const GemmEpilogue& e = g.epi;
   const int lane = threadIdx.x & 31;
@@ -374,9 +360,7 @@ __device__ __forceinline__ bool drain_tile_gate_reduce(uint32_t t_row, int m_w0,
   float gg[32], bb[32];
   load_f4_batch<8>(gate_row, nw, g.N, gg);
   load_f4_batch<8>(e.bias, nw, g.N, bb);
-  const long long c0 = wait_clk ? clock64() : 0;
   if (!mbar_wait_warp(tfull_bar, phase, wc, DEV_TIMEOUT_TMEM_FULL)) return false;
-  if (wait_clk) wait_clk[0] += clock64() - c0;
   tc_fence_after_sync();
   uint8_t* my_row = stage + lane * 128;
 #pragma unroll

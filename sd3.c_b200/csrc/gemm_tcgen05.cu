@@ -20,6 +20,9 @@
 #include <cudaTypedefs.h>
 #include <stdlib.h>
 
+#include <atomic>
+#include <mutex>
+
 #include "gemm_epilogue.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
@@ -198,16 +201,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 // host side
 // ------------------------------------------------------------------------------
 PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
-  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  // resolved once; the function-local static's initialisation is thread-safe
+  static const PFN_cuTensorMapEncodeTiled_v12000 fn = []() -> PFN_cuTensorMapEncodeTiled_v12000 {
     void* p = nullptr;
     cudaDriverEntryPointQueryResult q;
     cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
     if (e == cudaSuccess && q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
-  }
+      return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+    return nullptr;
+  }();
   return fn;
 }
 
@@ -265,16 +267,17 @@ int encode_tmap_3d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t 
 }
 
 int device_sm_count() {
-  static int sms[64] = {0};
+  static std::atomic<int> sms[64];  // zero-initialised; a racing first call computes the same value twice
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
-  if (sms[dev] == 0) {
-    int v = 0;
+  int v = sms[dev].load(std::memory_order_acquire);
+  if (v == 0) {
     cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-    sms[dev] = v > 0 ? v : 148;
+    if (v <= 0) v = 1;
+    sms[dev].store(v, std::memory_order_release);
   }
-  return sms[dev];
+  return v;
 }
 
 namespace {
@@ -284,14 +287,18 @@ int launch_inst(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmArgs& 
                 cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_tcgen05_kernel<BN, EPI, OUT_F32, FP8>;
+  static std::mutex attr_mutex;
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaError_t e =
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-    if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(gemm)");
-    attr_done[dev] = true;
+  if (dev >= 0 && dev < 64) {
+    std::lock_guard<std::mutex> lock(attr_mutex);
+    if (!attr_done[dev]) {
+      cudaError_t e =
+          cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+      if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(gemm)");
+      attr_done[dev] = true;
+    }
   }
   const int tiles = g.tiles_m * g.tiles_n;
   const int grid = tiles < device_sm_count() ? tiles : device_sm_count();
@@ -377,12 +384,8 @@ int launch_gemm(const void* A, long lda, const void* W, long ldw, int operand_dt
     set_last_error("gemm: table epilogue needs table and rows_in");
     return ST_INVALID_ARG;
   }
-  // Large bf16 problems go to the CTA-pair kernel (256 x 256 tiles across two SMs).
-  static const bool pair_enabled = []() {
-    const char* v = getenv("SD3_GEMM_PAIR");
-    return !(v && v[0] == '0');
-  }();
-  if (pair_enabled && gemm_pair_supported(operand_dtype, M, N, K, epi))
+  // Large problems go to the CTA-pair kernel (256 x 256 tiles across two SMs).
+  if (gemm_pair_supported(operand_dtype, M, N, K, epi))
     return launch_gemm_pair(A, lda, W, ldw, operand_dtype, M, N, K, epi, dev_status, stream);
 
   const int BN = (N >= 256 && N % 256 == 0) ? 256 : (N > 64 ? 128 : 64);

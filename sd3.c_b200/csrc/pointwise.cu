@@ -17,6 +17,8 @@
 
 namespace sd3 {
 
+int device_sm_count();
+
 namespace {
 
 // ----------------------------------------------------------------------------
@@ -160,7 +162,7 @@ int launch_ln_inst(const float* x, long rows, int T, int E, float eps, const flo
                    void* out2, long mod_stride, int out_f32, cudaStream_t stream) {
   // rows per warp: as many as keeps at least two CTAs per SM busy
   int rpw = LN_MAX_ROWS_PER_WARP;
-  while (rpw > 1 && (rows + LN_WARPS * rpw - 1) / (LN_WARPS * rpw) < 2L * 148) rpw >>= 1;
+  while (rpw > 1 && (rows + LN_WARPS * rpw - 1) / (LN_WARPS * rpw) < 2L * device_sm_count()) rpw >>= 1;
   const unsigned grid = static_cast<unsigned>((rows + LN_WARPS * rpw - 1) / (LN_WARPS * rpw));
   const bool dual = out2 != nullptr;
   const size_t smem = static_cast<size_t>(E) * 4 * (dual ? 4 : 2);
@@ -548,7 +550,7 @@ int launch_quantize_e4m3(const void* in, int in_f32, void* out, long n, float in
     return ST_INVALID_ARG;
   }
   const long blocks = (n / 4 + 255) / 256;
-  const unsigned grid = static_cast<unsigned>(blocks < 148 * 16 ? blocks : 148 * 16);
+  const unsigned grid = static_cast<unsigned>(blocks < device_sm_count() * 16 ? blocks : device_sm_count() * 16);
   if (in_f32)
     quantize_e4m3_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(in),
                                                           static_cast<uint8_t*>(out), n, inv_scale);
@@ -566,7 +568,7 @@ int launch_absmax(const void* in, int in_f32, long n, float* out, cudaStream_t s
   cudaError_t e = cudaMemsetAsync(out, 0, 4, stream);
   if (e != cudaSuccess) return check_cuda(e, "cudaMemsetAsync(absmax)");
   const long blocks = (n + 255) / 256;
-  const unsigned grid = static_cast<unsigned>(blocks < 148 * 8 ? blocks : 148 * 8);
+  const unsigned grid = static_cast<unsigned>(blocks < device_sm_count() * 8 ? blocks : device_sm_count() * 8);
   if (in_f32)
     absmax_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(in), n,
                                                    reinterpret_cast<unsigned*>(out));
@@ -578,14 +580,14 @@ int launch_absmax(const void* in, int in_f32, long n, float* out, cudaStream_t s
 
 int launch_cast_f32_to_bf16(const float* in, bf16* out, long n, cudaStream_t stream) {
   if (n <= 0) return ST_OK;
-  const unsigned grid = static_cast<unsigned>(n / 256 + 1 < 148 * 16 ? n / 256 + 1 : 148 * 16);
+  const unsigned grid = static_cast<unsigned>(n / 256 + 1 < device_sm_count() * 16 ? n / 256 + 1 : device_sm_count() * 16);
   cast_kernel<float, bf16><<<grid, 256, 0, stream>>>(in, out, n);
   return after_launch("cast_kernel");
 }
 
 int launch_cast_bf16_to_f32(const bf16* in, float* out, long n, cudaStream_t stream) {
   if (n <= 0) return ST_OK;
-  const unsigned grid = static_cast<unsigned>(n / 256 + 1 < 148 * 16 ? n / 256 + 1 : 148 * 16);
+  const unsigned grid = static_cast<unsigned>(n / 256 + 1 < device_sm_count() * 16 ? n / 256 + 1 : device_sm_count() * 16);
   cast_kernel<bf16, float><<<grid, 256, 0, stream>>>(in, out, n);
   return after_launch("cast_kernel");
 }

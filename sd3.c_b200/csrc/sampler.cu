@@ -10,6 +10,10 @@
 #include "../../include/sd3_b200.h"
 #include "kernels.h"
 
+namespace sd3 {
+int device_sm_count();
+}
+
 namespace {
 
 template <typename T>
@@ -51,7 +55,7 @@ extern "C" int sd3_cfg_euler_step(float* x_state, void* x_stacked, const void* v
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const long blocks = (half_elems + 255) / 256;
-  const unsigned grid = static_cast<unsigned>(blocks < 148 * 8 ? blocks : 148 * 8);
+  const unsigned grid = static_cast<unsigned>(blocks < sd3::device_sm_count() * 8 ? blocks : sd3::device_sm_count() * 8);
   if (io_dtype == SD3_DTYPE_F32)
     cfg_euler_kernel<float><<<grid, 256, 0, st>>>(x_state, static_cast<float*>(x_stacked),
                                                   static_cast<const float*>(v_stacked), half_elems,

@@ -257,3 +257,30 @@ def test_model_golden_fp8_mode(sd3):
     print("fp8 toy rel_l2", r)
     assert r < 1e-1
     m.close()
+
+
+def test_fp8_weights_requantised_after_set_param(sd3):
+    """In FP8 mode a weight rewritten after finalize gets a fresh e4m3 twin at the next
+    finalize: the model then gives the same bits as one built with that weight."""
+    g = golden("model_toy.pt")
+    p = to_dev(g["params"], torch.bfloat16)
+    args = (g["pooled"].bfloat16().cuda(), g["captions"].bfloat16().cuda(), g["latent"].bfloat16().cuda(),
+            g["timesteps"].cuda())
+    name = "transformer.0.latent_mlp.lin1.weight"
+    other = (torch.randn_like(p[name].float()) * 0.05).bfloat16()
+    m = make_model(sd3, g["config"], g["params"], sd3.PRECISION_FP8)
+    out_a = m.forward(*args).clone()
+    m.set_param(name, other)
+    m.load({})  # finalize again
+    out_b = m.forward(*args).clone()
+    torch.cuda.synchronize()
+    m.close()
+    p2 = dict(g["params"])
+    p2[name] = other.cpu()
+    m2 = make_model(sd3, g["config"], p2, sd3.PRECISION_FP8)
+    out_c = m2.forward(*args)
+    torch.cuda.synchronize()
+    assert sd3.device_status() == 0
+    m2.close()
+    assert not torch.equal(out_a, out_b)
+    assert torch.equal(out_b, out_c)
