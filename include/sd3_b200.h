@@ -157,6 +157,13 @@ SD3_API int sd3_sinusoidal_embedding(const float* t, float* out, int B, int dim,
 SD3_API int sd3_pos_embed_table(float* table, int h, int w, int E, int pos_max, int base_size,
                         void* stream);
 
+/* Self-test of the device-side timeout path: launches a kernel whose only work is a
+ * bounded wait (limit_us microseconds) on a barrier nobody arrives on.  After
+ * the stream has drained, sd3_device_status reports code 199 once and clears
+ * it; calls made afterwards are unaffected.  No counterpart in the reference,
+ * which exits the process on CUDA errors (cuda/dit.cu:96,460,690,738). */
+SD3_API int sd3_selftest_wait_timeout(int limit_us, void* stream);
+
 /* Patch embedding: x[b, r*w+s, :] = conv(latent; kernel=stride=patch)[b,:,r,s]
  * + bias + pos_table[r*w+s, :].  latent (B,C,H,W) of io_dtype, w_nk bf16
  * (E, C*p*p), out (B*h*w, E) f32; scratch holds B*h*w*C*p*p bf16.
@@ -170,10 +177,10 @@ SD3_API int sd3_patch_embed(const void* latent, int io_dtype, const void* w_nk_b
  * PatchEmbedding, modules.cpp:1093-1117, allocates its temporaries with new[]).
  *
  * Who needs it: callers that cannot call cudaMalloc at the point where they
- * run the operator -- e.g. while a stream is being captured into a CUDA graph
- * (allocation is not allowed during capture), inside latency-critical serving
- * loops (cudaMalloc/cudaFree synchronise the device), or under a host that
- * fixes the memory budget when the library is loaded.
+ * run the operator -- latency-critical serving loops (cudaMalloc and cudaFree
+ * synchronise the whole device), hosts that fix the memory budget when the
+ * library is loaded, and code that runs where the allocator must not be
+ * entered at all.
  *
  * Same arguments and result as sd3_patch_embed minus `scratch`: the gathered
  * patches go to a fixed array of SD3_STATIC_PATCH_ELEMS bf16 elements (8 MiB)
@@ -184,8 +191,9 @@ SD3_API int sd3_patch_embed(const void* latent, int io_dtype, const void* w_nk_b
  * calls whose GPU work overlaps race on it and must be serialised by the
  * caller.  The first call on a device resolves the array's device address;
  * issue that first call before any stream capture.  No cudaMalloc, cudaFree
- * or allocating library routine is called, and no device status word is
- * attached (bounded waits still apply). */
+ * or allocating library routine is called.  A bounded device wait that runs
+ * out during such a call is recorded in a word next to the array, which
+ * sd3_device_status reads and clears along with the ordinary status word. */
 #define SD3_STATIC_PATCH_ELEMS (4L * 1024 * 1024)
 SD3_API int sd3_patch_embed_static(const void* latent, int io_dtype, const void* w_nk_bf16,
                                    const float* bias, const float* pos_table, float* out, int B,

@@ -31,7 +31,7 @@ def sinusoidal_embedding(t, dim=256):
     """get_sinusoidal_embedding, module_tests/modules.py:70-77 (cos first)."""
     half = dim // 2
     freqs = torch.exp(-9.2103403719761836 * torch.arange(half, dtype=torch.float32) / half)[None, :]
-    a = t.to(torch.float32)[:, None] * freqs
+    a = t.to(torch.float32)[:, None] * freqs.to(t.device)
     return torch.cat([torch.cos(a), torch.sin(a)], dim=1)
 
 
@@ -62,7 +62,7 @@ def patch_embed(latent, conv_w, conv_b, pos_max, base_height, patch):
     x = F.conv2d(latent, conv_w, conv_b, stride=patch)
     B, E, h, w = x.shape
     x = x.flatten(2).transpose(1, 2)
-    pe = pos_embed_cropped(E, h, w, pos_max, base_height // patch).to(x.dtype)
+    pe = pos_embed_cropped(E, h, w, pos_max, base_height // patch).to(device=x.device, dtype=x.dtype)
     return x + pe
 
 
@@ -193,7 +193,7 @@ def dit_forward(pooled, captions, latent, timesteps, p, num_layers, dual_attenti
 
 
 # ---------------------------------------------------------------------------
-# seeded synthetic parameters / inputs (shapes of BASELINE configs)
+# seeded synthetic parameters / inputs (SD3.5-medium shapes)
 # ---------------------------------------------------------------------------
 def block_param_shapes(E, mlp_expand, head_dim, dual, discard_context, qk_norm=True):
     """name -> shape in the boundary layout ((in, out) for 2-D weights)."""

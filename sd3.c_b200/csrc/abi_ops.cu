@@ -9,6 +9,8 @@ namespace sd3 {
 
 // One status word per device, allocated on first use and kept for the life of
 // the process.  Kernels write a DEV_TIMEOUT_* code there when a wait runs out.
+int* static_status_word_if_resolved();
+
 int* device_status_word() {
   static int* words[64] = {nullptr};
   static std::mutex mu;
@@ -58,6 +60,15 @@ int sd3_device_status(int* status_out) {
   if (*status_out != 0) {
     set_last_error("a kernel gave up a bounded wait (device status %d)", *status_out);
     return check_cuda(cudaMemset(w, 0, sizeof(int)), "status clear");
+  }
+  // the allocation-free entry point records into a word of its own
+  if (int* ws = static_status_word_if_resolved()) {
+    rc = check_cuda(cudaMemcpy(status_out, ws, sizeof(int), cudaMemcpyDeviceToHost), "status read");
+    if (rc) return rc;
+    if (*status_out != 0) {
+      set_last_error("a kernel gave up a bounded wait (device status %d)", *status_out);
+      return check_cuda(cudaMemset(ws, 0, sizeof(int)), "status clear");
+    }
   }
   return SD3_OK;
 }

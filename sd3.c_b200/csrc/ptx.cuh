@@ -28,6 +28,7 @@ enum : int {
   DEV_TIMEOUT_ATTN_O = 113,
   DEV_TIMEOUT_ATTN_KV = 114,
   DEV_TIMEOUT_ATTN_Q = 115,
+  DEV_TIMEOUT_SELFTEST = 199,  // the self-test kernel's wait on a barrier nobody arrives on
 };
 
 #ifndef SD3_WAIT_LIMIT_NS
@@ -122,7 +123,7 @@ struct WaitCtx {
 // Bounded wait.  Returns false when the wait ran out or another role of the
 // CTA already aborted; the caller must then stop issuing work.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w,
-                                          int code) {
+                                          int code, uint64_t limit_ns = SD3_WAIT_LIMIT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   uint32_t it = 0;
@@ -130,7 +131,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
     if (mbar_try_wait(bar, parity)) return true;
     if (((++it) & 0xffu) == 0) {
       if (*w.s_abort) return false;
-      if (global_timer_ns() - t0 > SD3_WAIT_LIMIT_NS) {
+      if (global_timer_ns() - t0 > limit_ns) {
         *w.s_abort = 1;
         if (w.g_status) atomicCAS(w.g_status, 0, code);
         return false;

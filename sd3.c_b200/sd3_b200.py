@@ -82,6 +82,7 @@ PROTOTYPES = {
     "sd3_block_forward": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "sd3_cfg_euler_step": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_long, c_float, c_float, c_void_p]),
     "sd3_launch_count": (c_long, [c_int]),
+    "sd3_selftest_wait_timeout": (c_int, [c_int, c_void_p]),
 }
 
 _lib = None
@@ -296,6 +297,17 @@ def patch_embed_static(latent, w_nk_bf16, bias, pos_table, patch, E, out=None):
     hp, wp = H // patch, W // patch
     if out is None:
         out = torch.empty((B * hp * wp, E), device=latent.device, dtype=torch.float32)
+    # the C side only sees pointers: shapes, dtypes and devices are checked here
+    if (out.dtype != torch.float32 or out.numel() != B * hp * wp * E or not out.is_contiguous()
+            or out.device != latent.device):
+        raise Sd3Error("patch_embed_static: out must be a contiguous float32 tensor of %d elements on %s"
+                       % (B * hp * wp * E, latent.device))
+    if tuple(w_nk_bf16.shape) != (E, C * patch * patch) or w_nk_bf16.dtype != torch.bfloat16:
+        raise Sd3Error("patch_embed_static: weight must be bfloat16 of shape (%d, %d)" % (E, C * patch * patch))
+    if tuple(pos_table.shape) != (hp * wp, E) or pos_table.dtype != torch.float32:
+        raise Sd3Error("patch_embed_static: pos_table must be float32 of shape (%d, %d)" % (hp * wp, E))
+    if bias is not None and (bias.numel() != E or bias.dtype != torch.float32):
+        raise Sd3Error("patch_embed_static: bias must be float32 with %d elements" % E)
     check(lib().sd3_patch_embed_static(ptr(latent), dtype_tag(latent), ptr(w_nk_bf16), ptr(bias),
                                        ptr(pos_table), ptr(out), B, C, H, W, patch, E,
                                        stream_ptr()), "sd3_patch_embed_static")

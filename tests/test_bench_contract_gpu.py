@@ -22,14 +22,15 @@ def _run(args, timeout=900):
 
 
 def test_bench_line_of_this_arm():
-    d = _run(["--steps", "2", "--warmup", "3", "--no-cpu-baseline"])
+    d = _run(["--steps", "2", "--warmup", "3", "--no-cpu-baseline", "--no-extras"])
     for k in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better",
               "scaling", "vs_baseline", "dtype", "data", "config", "e2e", "gpu_launches", "clocks", "roofline"):
         assert k in d, k
     assert d["metric"].startswith("SD3.5-M DiT denoise steps/sec") and d["unit"] == "steps/s"
     assert d["n_gpus"] == 1 and d["steps"] == 2 and d["warmup"] >= 3 and d["higher_is_better"] is True
-    assert d["dtype"] == "bf16" and d["data"] == "synthetic" and d["scaling"] == "weak"
-    assert "workload" in d["config"] and "model" not in d["config"]
+    assert d["dtype"] == "bf16" and d["data"] == "synthetic" and d["scaling"] == "strong"
+    assert "workload" in d["config"] and "model" not in d["config"] and d["config"]["per_gpu_batch"] == 8
+    assert abs(d["weak_value"] - d["value"]) < 1e-9  # one GPU: the two readings coincide
     assert abs(d["value"] * d["ms_per_step"] - 1000.0) < 1e-6 * 1000.0
     assert d["gpu_launches"] >= 2 * 300  # ~360 kernels per step
     e = d["e2e"]
@@ -41,6 +42,7 @@ def test_bench_line_of_this_arm():
     assert abs(r["frac"] - r["achieved"] / r["peak"]) < 1e-3 and r["traffic"] > 0
     assert {"sm_mhz", "sm_max_mhz", "reasons"} <= set(d["clocks"])
     assert len(d["kernels"]) >= 8
+    assert any(k["kernel"].startswith("[library, context only]") for k in d["kernels"])
 
 
 def test_bench_line_of_the_reference_arm():
@@ -51,3 +53,5 @@ def test_bench_line_of_the_reference_arm():
     assert c["kind"] in ("port", "reference") and c["cores"] >= 1 and c["value"] == d["value"] and c["sample"]
     e = d["e2e"]
     assert e["value"] == d["value"] and e["h2d_bytes_per_step"] == 0 and e["d2h_bytes_per_step"] == 0
+    assert abs(d["value"] * d["full_batch_forward_s"] - 1.0) < 1e-6 and d["ms_per_step"] > 0
+    assert d["config"]["workload"].startswith("SD3.5-medium DiT forward, 1024^2, batch 8")

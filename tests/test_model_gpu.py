@@ -108,7 +108,7 @@ def test_missing_and_unknown_parameters(sd3):
 
 
 def test_config1_single_dual_block_fp32(sd3):
-    """BASELINE config 1: one dual MMDiT-X block, fp32, batch 1, E 1536, 24 heads,
+    """One dual MMDiT-X block, fp32, batch 1, E 1536, 24 heads,
     256 image + 77 context tokens, weights N(0, 0.02), biases 0, seed 0; the
     conditioning vector comes from a timestep-500 sinusoidal embedding plus a
     pooled N(0,1) vector through SiLU."""
@@ -148,7 +148,7 @@ def test_config1_single_dual_block_fp32(sd3):
 
 
 def test_config2_full_model_bf16(sd3):
-    """BASELINE config 2: full SD3.5-medium DiT forward, bf16, batch 1, 512x512
+    """Full SD3.5-medium DiT forward, bf16, batch 1, 512x512
     (latent 16x64x64 -> 1024 image tokens), 333 context tokens x 4096, pooled
     2048, 24 blocks (first 13 dual), weights N(0, 0.02), seed 1.  Checked
     against the fp32 CPU oracle on the same bf16-rounded weights and inputs."""
@@ -218,7 +218,7 @@ def _block_case(sd3, B, Tx, Tc, seed, dual):
 
 
 def test_config3_block_full_size_and_batch_independence(sd3):
-    """BASELINE config 3 shapes (batch 8, 4096 image + 333 context tokens), one
+    """The benchmark shapes (batch 8, 4096 image + 333 context tokens), one
     dual block: parity with the oracle, and the size-independent property the
     path offers: samples never interact, so sample b of the batch-8 call has
     the same bits as a batch-1 call on that sample."""
@@ -234,7 +234,7 @@ def test_config3_block_full_size_and_batch_independence(sd3):
 
 
 def test_config5_block_long_sequence(sd3):
-    """BASELINE config 5 shapes: one 2048x2048 image, 16384 image + 333 context
+    """One 2048x2048 image, 16384 image + 333 context
     tokens (131 key tiles per attention row), one plain block, batch 1."""
     m, _, (xx, cc), (x_ref, c_ref) = _block_case(sd3, 1, 16384, 333, seed=4, dual=False)
     assert rel_l2(xx, x_ref.cpu()) < 1e-2
@@ -284,3 +284,55 @@ def test_fp8_weights_requantised_after_set_param(sd3):
     m2.close()
     assert not torch.equal(out_a, out_b)
     assert torch.equal(out_b, out_c)
+
+
+def _full_model_case(sd3, B, HW, seed, bar=1e-2):
+    """Full SD3.5-medium denoiser forward in bf16 against the oracle run in fp32 on the
+    GPU (TF32 off) on the same bf16-rounded weights and inputs (math of
+    module_tests/modules.py:397-425)."""
+    cfgm = O.SD35_MEDIUM
+    shapes = O.model_param_shapes(cfgm["num_layers"], cfgm["dual_layers"], cfgm["in_dim"], cfgm["E"],
+                                  cfgm["pooled_dim"], cfgm["captions_dim"], cfgm["patch"],
+                                  cfgm["attn_heads"], cfgm["mlp_expand"])
+    p = O.random_params(shapes, seed=seed, std=0.02, dtype=torch.bfloat16)
+    gen = torch.Generator().manual_seed(seed)
+    latent = torch.randn(B, 16, HW, HW, generator=gen).bfloat16()
+    captions = torch.randn(B, 333, 4096, generator=gen).bfloat16()
+    pooled = torch.randn(B, 2048, generator=gen).bfloat16()
+    t = (torch.rand(B, generator=gen) * 1000).bfloat16().float()
+    m = sd3.Model(24, range(13), 2048, 4096, 16, 1536, 24, 4, 2, 384, 128, True, sd3.PRECISION_BF16)
+    m.load({k: v.cuda() for k, v in p.items()})
+    out = m.forward(pooled.cuda(), captions.cuda(), latent.cuda(), t.cuda())
+    torch.cuda.synchronize()
+    assert sd3.device_status() == 0
+    m.close()
+    del m
+    torch.cuda.empty_cache()
+    tf32 = (torch.backends.cuda.matmul.allow_tf32, torch.backends.cudnn.allow_tf32)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    try:
+        with torch.no_grad():
+            pf = {k: v.float().cuda() for k, v in p.items()}
+            ref = O.dit_forward(pooled.float().cuda(), captions.float().cuda(), latent.float().cuda(), t.cuda(),
+                                pf, 24, range(13), 24, 2, 384, 128, True)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32, torch.backends.cudnn.allow_tf32 = tf32
+    r = rel_l2(out, ref)
+    print("full model B %d %dx%d rel_l2 %.3e" % (B, HW, HW, r))
+    assert r < bar
+    del pf, ref
+    torch.cuda.empty_cache()
+
+
+def test_full_model_1024px_batch2_bf16(sd3):
+    """The forward the benchmark times (1024x1024: latent 16x128x128 -> 4096 image tokens
+    + 333 context tokens, 24 chained blocks), at batch 2 so that the fp32 oracle stays
+    quick; samples never interact, so batch 8 is four of these."""
+    _full_model_case(sd3, 2, 128, seed=2)
+
+
+def test_full_model_2048px_long_sequence_bf16(sd3):
+    """One 2048x2048 image: latent 16x256x256 -> 16384 image tokens + 333 context tokens
+    through the whole denoiser on one GPU."""
+    _full_model_case(sd3, 1, 256, seed=4)

@@ -1,5 +1,5 @@
-"""Sampling loop (Euler flow matching + classifier-free guidance, BASELINE
-config 4 in miniature): the fused update kernel and the loop around the
+"""Sampling loop (Euler flow matching + classifier-free guidance, in
+miniature): the fused update kernel and the loop around the
 denoiser against the CPU oracle's loop on the toy golden model."""
 import pytest
 import torch

@@ -1,7 +1,7 @@
 """sd3_patch_embed_static: the allocation-free variant of the patch-embedding
-operator, for callers that cannot call cudaMalloc where they run it (stream
-capture, allocator-free serving loops, fixed memory budgets).  Its scratch is a
-fixed array inside the library, shared by all calls on a device.
+operator, for callers that cannot call cudaMalloc where they run it
+(allocator-free serving loops, fixed memory budgets).  Its scratch is a fixed
+array inside the library, shared by all calls on a device.
 
 This file is collected last on purpose: a run that stops at the first failure
 has then already executed every other test.  The test passes on its own in a
@@ -49,3 +49,29 @@ def test_static_scratch_rejects_oversized_problems(sd3):
                                           sd3.ptr(out), B, C, H, W, 2, E, sd3.stream_ptr())
     assert rc == -2
     assert b"built-in scratch" in sd3.lib().sd3_last_error()
+
+
+def test_static_call_allocates_nothing_once_warm(sd3):
+    # after one warm call (symbol addresses, kernel attributes and the tensor-map entry
+    # point resolved) a call with a preallocated output leaves the allocator untouched
+    lat, w, b, pt = _inputs(7, 2, 16, 32, 32, 256, 2, sd3)
+    out = torch.empty(2 * 16 * 16, 256, device="cuda")
+    sd3.patch_embed_static(lat, w, b, pt, 2, 256, out=out)
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    alloc0 = torch.cuda.memory_allocated()
+    sd3.patch_embed_static(lat, w, b, pt, 2, 256, out=out)
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == alloc0
+    assert torch.cuda.mem_get_info()[0] == free0  # the driver's view: nothing was allocated or freed
+    assert torch.equal(out, sd3.patch_embed(lat, w, b, pt, 2, 256))
+
+
+def test_static_binding_validates_tensors(sd3):
+    lat, w, b, pt = _inputs(8, 1, 16, 16, 16, 128, 2, sd3)
+    with pytest.raises(sd3.Sd3Error):  # output too small
+        sd3.patch_embed_static(lat, w, b, pt, 2, 128, out=torch.empty(10, 128, device="cuda"))
+    with pytest.raises(sd3.Sd3Error):  # wrong dtype
+        sd3.patch_embed_static(lat, w, b, pt, 2, 128, out=torch.empty(64, 128, device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(sd3.Sd3Error):  # weight of the wrong shape
+        sd3.patch_embed_static(lat, w[:, :32].contiguous(), b, pt, 2, 128)
