@@ -307,6 +307,27 @@ int run_linear(sd3_model* m, const Linear& L, const void* A, int M, const GemmEp
   return launch_gemm(A, L.K, L.w, L.K, OPERAND_BF16, M, L.N, L.K, ee, m->status, st);
 }
 
+// Two linears of the same shape class (the image-stream GEMM and its context-stream twin) as
+// one grouped launch where the tensor-core path takes both; otherwise one after the other.
+int run_linear_pair(sd3_model* m, const Linear& La, const void* Aa, int Ma, const GemmEpilogue& ea, bool a8a,
+                    const Linear& Lb, const void* Ab, int Mb, const GemmEpilogue& eb, bool a8b, cudaStream_t st) {
+  const bool fp8a = m->fp8 && La.w8 && a8a, fp8b = m->fp8 && Lb.w8 && a8b;
+  const bool plain_a = !(m->fp8 && La.w8) && !a8a, plain_b = !(m->fp8 && Lb.w8) && !a8b;
+  const bool same_kind = (fp8a && fp8b) || (plain_a && plain_b);
+  if (m->f32 || !La.w || !Lb.w || La.N != Lb.N || La.K != Lb.K || !same_kind) {
+    int rc = run_linear(m, La, Aa, Ma, ea, st, a8a);
+    if (rc) return rc;
+    return run_linear(m, Lb, Ab, Mb, eb, st, a8b);
+  }
+  GemmProblem pa, pb;
+  pa.A = Aa; pa.lda = La.K; pa.W = fp8a ? La.w8 : La.w; pa.ldw = La.K; pa.M = Ma; pa.epi = ea;
+  pb.A = Ab; pb.lda = Lb.K; pb.W = fp8b ? Lb.w8 : Lb.w; pb.ldw = Lb.K; pb.M = Mb; pb.epi = eb;
+  if (!pa.epi.bias) pa.epi.bias = La.b;
+  if (!pb.epi.bias) pb.epi.bias = Lb.b;
+  if (fp8a) { pa.epi.alpha = La.wscale; pb.epi.alpha = Lb.wscale; }
+  return launch_gemm_grouped(pa, pb, fp8a ? OPERAND_E4M3 : OPERAND_BF16, La.N, La.K, m->status, st);
+}
+
 // QKV projection of `T_in` tokens per sample into rows [row_off, row_off+T_in)
 // of each sample of the packed (B, T_total, 3E) buffer, q/k RMSNorm included.
 int run_qkv(sd3_model* m, const Linear& L, const void* h, void* qkv, int B, int T_in, int T_total,
@@ -375,6 +396,28 @@ int run_mlp1(sd3_model* m, const Linear& L, const Linear& next, const void* A, i
   return run_linear(m, L, A, M, e, st, a_e4m3);
 }
 
+GemmEpilogue qkv_epilogue(sd3_model* m, void* qkv, int T_in, int T_total, int row_off, const float* wq,
+                          const float* wk) {
+  GemmEpilogue e;
+  e.mode = EPI_QKV_NORM;
+  e.out = qkv;
+  e.out_f32 = 0;
+  e.ldo = 3L * m->E;
+  e.rows_in = T_in; e.rows_out = T_total; e.row_off = row_off;
+  e.wq = wq; e.wk = wk; e.qk_cols = 2 * m->E; e.eps = 1e-6f;
+  e.do_norm = (m->cfg.use_qk_norm && (wq || wk)) ? 1 : 0;
+  return e;
+}
+
+GemmEpilogue gate_epilogue(const Linear& L, int Tseg, const float* gate, long mod_stride, float* resid) {
+  GemmEpilogue e;
+  e.mode = EPI_GATE_RESID;
+  e.out = resid; e.resid = resid; e.out_f32 = 1; e.ldo = L.N;
+  e.gate = gate; e.gate_stride = mod_stride;
+  e.rows_in = Tseg; e.rows_out = Tseg; e.row_off = 0;
+  return e;
+}
+
 int block_body(sd3_model* m, int l, float* c, float* x, int B, int Tc, int Tx, const float* mod,
                long ms, cudaStream_t st) {
   const LayerW& L = m->layers[l];
@@ -410,32 +453,56 @@ int block_body(sd3_model* m, int l, float* c, float* x, int B, int Tc, int Tx, c
     SD3_TRY(launch_ln_modulate(x, B, Tx, E, 1e-6f, x_shift_a, x_scale_a, w.h_x, nullptr, nullptr,
                                nullptr, ms, ln_out(x8a), st));
   // QKV (context rows first, then image rows) and joint attention
-  SD3_TRY(run_qkv(m, L.c_qkv, w.h_c, w.qkv, B, Tc, T, 0, L.c_wq, L.c_wk, st, c8a));
-  SD3_TRY(run_qkv(m, L.x_qkv, w.h_x, w.qkv, B, Tx, T, Tc, L.x_wq, L.x_wk, st, x8a));
+  // the tensor-core path (bf16 / FP8 modes, head_dim 64): image and context GEMMs of a kind share a launch
+  const bool grouped = !m->f32 && m->D == 64;
+  if (grouped) {
+    SD3_TRY(run_linear_pair(m, L.x_qkv, w.h_x, B * Tx, qkv_epilogue(m, w.qkv, Tx, T, Tc, L.x_wq, L.x_wk), x8a,
+                            L.c_qkv, w.h_c, B * Tc, qkv_epilogue(m, w.qkv, Tc, T, 0, L.c_wq, L.c_wk), c8a, st));
+  } else {
+    SD3_TRY(run_qkv(m, L.c_qkv, w.h_c, w.qkv, B, Tc, T, 0, L.c_wq, L.c_wk, st, c8a));
+    SD3_TRY(run_qkv(m, L.x_qkv, w.h_x, w.qkv, B, Tx, T, Tc, L.x_wq, L.x_wk, st, x8a));
+  }
   // FP8 mode: both out-projections of the joint attention must take e4m3 for the
   // kernel to write it (one flag for both outputs)
   const bool o8 = m->fp8 && m->D == 64 && L.x_out.w8 && (L.last || L.c_out.w8);
   SD3_TRY(run_attention(m, w.qkv, B, T, Tc, L.last ? nullptr : w.o_c, w.o_x, st, o8));
-  if (!L.last) SD3_TRY(run_gate_resid(m, L.c_out, w.o_c, B, Tc, c_gate_a, ms, c, st, o8));
-  SD3_TRY(run_gate_resid(m, L.x_out, w.o_x, B, Tx, x_gate_a, ms, x, st, o8));
+  if (grouped && !L.last) {
+    SD3_TRY(run_linear_pair(m, L.x_out, w.o_x, B * Tx, gate_epilogue(L.x_out, Tx, x_gate_a, ms, x), o8,
+                            L.c_out, w.o_c, B * Tc, gate_epilogue(L.c_out, Tc, c_gate_a, ms, c), o8, st));
+  } else {
+    if (!L.last) SD3_TRY(run_gate_resid(m, L.c_out, w.o_c, B, Tc, c_gate_a, ms, c, st, o8));
+    SD3_TRY(run_gate_resid(m, L.x_out, w.o_x, B, Tx, x_gate_a, ms, x, st, o8));
+  }
   if (L.dual) {
     SD3_TRY(run_qkv(m, L.d_qkv, w.h_x2, w.qkv2, B, Tx, Tx, 0, L.d_wq, L.d_wk, st, x8a));
     const bool o8d = m->fp8 && m->D == 64 && L.d_out.w8;
     SD3_TRY(run_attention(m, w.qkv2, B, Tx, 0, nullptr, w.o_x2, st, o8d));
     SD3_TRY(run_gate_resid(m, L.d_out, w.o_x2, B, Tx, x_gate_2, ms, x, st, o8d));
   }
-  // image MLP
-  bool hid8 = false;
+  // MLPs of both streams: LayerNorm + modulate each, then the two first linears (GELU-tanh) and
+  // the two second linears (gate + residual), each pair as one grouped launch
   SD3_TRY(launch_ln_modulate(x, B, Tx, E, 1e-6f, x_shift_m, x_scale_m, w.h_x, nullptr, nullptr,
                              nullptr, ms, ln_out(x8m), st));
-  SD3_TRY(run_mlp1(m, L.x_mlp1, L.x_mlp2, w.h_x, B * Tx, w.hid_x, st, x8m, &hid8));
-  SD3_TRY(run_gate_resid(m, L.x_mlp2, w.hid_x, B, Tx, x_gate_m, ms, x, st, hid8));
-  // context MLP
-  if (!L.last) {
+  if (!L.last)
     SD3_TRY(launch_ln_modulate(c, B, Tc, E, 1e-6f, c_shift_m, c_scale_m, w.h_c, nullptr, nullptr,
                                nullptr, ms, ln_out(c8m), st));
-    SD3_TRY(run_mlp1(m, L.c_mlp1, L.c_mlp2, w.h_c, B * Tc, w.hid_c, st, c8m, &hid8));
-    SD3_TRY(run_gate_resid(m, L.c_mlp2, w.hid_c, B, Tc, c_gate_m, ms, c, st, hid8));
+  if (grouped && !L.last) {
+    const bool hx8 = m->fp8 && L.x_mlp1.w8 && L.x_mlp2.w8 && L.x_mlp1.N % 64 == 0;
+    const bool hc8 = m->fp8 && L.c_mlp1.w8 && L.c_mlp2.w8 && L.c_mlp1.N % 64 == 0;
+    GemmEpilogue ex, ec;
+    ex.mode = EPI_BIAS_GELU; ex.out = w.hid_x; ex.out_f32 = 0; ex.ldo = L.x_mlp1.N; ex.out_e4m3 = hx8 ? 1 : 0;
+    ec.mode = EPI_BIAS_GELU; ec.out = w.hid_c; ec.out_f32 = 0; ec.ldo = L.c_mlp1.N; ec.out_e4m3 = hc8 ? 1 : 0;
+    SD3_TRY(run_linear_pair(m, L.x_mlp1, w.h_x, B * Tx, ex, x8m, L.c_mlp1, w.h_c, B * Tc, ec, c8m, st));
+    SD3_TRY(run_linear_pair(m, L.x_mlp2, w.hid_x, B * Tx, gate_epilogue(L.x_mlp2, Tx, x_gate_m, ms, x), hx8,
+                            L.c_mlp2, w.hid_c, B * Tc, gate_epilogue(L.c_mlp2, Tc, c_gate_m, ms, c), hc8, st));
+  } else {
+    bool hid8 = false;
+    SD3_TRY(run_mlp1(m, L.x_mlp1, L.x_mlp2, w.h_x, B * Tx, w.hid_x, st, x8m, &hid8));
+    SD3_TRY(run_gate_resid(m, L.x_mlp2, w.hid_x, B, Tx, x_gate_m, ms, x, st, hid8));
+    if (!L.last) {
+      SD3_TRY(run_mlp1(m, L.c_mlp1, L.c_mlp2, w.h_c, B * Tc, w.hid_c, st, c8m, &hid8));
+      SD3_TRY(run_gate_resid(m, L.c_mlp2, w.hid_c, B, Tc, c_gate_m, ms, c, st, hid8));
+    }
   }
 #undef SD3_TRY
   return ST_OK;

@@ -1,6 +1,11 @@
 // CTA-pair variant of the tcgen05 GEMM: two CTAs (a cluster of two on
-// neighbouring SMs) cooperate on 256 x 256 output tiles with
-// tcgen05.mma.cta_group::2.
+// neighbouring SMs) cooperate on 256 x 256 (or, for problems with too few of
+// those to fill the machine, 256 x 128) output tiles with
+// tcgen05.mma.cta_group::2.  One launch can carry TWO problems of the same
+// shape class (same N, K and epilogue: the image-stream GEMM of a block and its
+// small context-stream twin); the persistent tile loop runs the first problem's
+// tiles and then the second's, so the small one rides in the tail of the large
+// one instead of being a launch of its own that fills less than a wave.
 //
 //   acc[m, n] = sum_k A[m, k] * W[n, k]        A: (M, K) K-major, W: (N, K) K-major
 //
@@ -34,46 +39,51 @@ namespace {
 using namespace gemm_detail;
 
 constexpr int P_BM = 128;            // rows of A per CTA (256 per pair)
-constexpr int P_BN = 256;            // output columns per pair tile
-constexpr int P_BN_HALF = 128;       // rows of W each CTA loads
 constexpr int P_KBYTES = 128;        // bytes of K per stage row (64 bf16)
 constexpr int P_A_BYTES = P_BM * P_KBYTES;
-constexpr int P_B_BYTES = P_BN_HALF * P_KBYTES;
-constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;  // 32 KiB
-// Stages of the operand ring: seven of 32 KiB, or six where the epilogue needs shared
-// memory of its own (gate + residual: 4 KiB per epilogue warp for the TMA reduction).
+// PBN = output columns per pair tile (256 or 128); each CTA loads PBN / 2 rows of W
+__host__ __device__ constexpr int pair_b_bytes(int pbn) { return (pbn / 2) * P_KBYTES; }
+__host__ __device__ constexpr int pair_stage_bytes(int pbn) { return P_A_BYTES + pair_b_bytes(pbn); }  // 32 / 24 KiB
+// The epilogues that leave through shared memory (TMA reduction or TMA store) get 4 KiB per
+// epilogue warp.
 constexpr int P_RED_BYTES = 4096;
 __host__ __device__ constexpr bool pair_stages_out(int epi, bool out_f32) {
   return epi == EPI_GATE_RESID || (!out_f32 && (epi == EPI_BIAS || epi == EPI_BIAS_GELU || epi == EPI_QKV_NORM));
 }
-// Six stages everywhere: they are handed over in SLOTS of two (one full/empty barrier pair,
-// one barrier test and one tcgen05.commit per 64 KiB instead of per 32 KiB: the issuing
+// Six stages of 32 KiB (eight of 24 KiB), handed over in SLOTS of two (one full/empty barrier
+// pair, one barrier test and one tcgen05.commit per slot instead of per stage: the issuing
 // thread spent ~100 of every 680 cycles of a stage on those two).
-__host__ __device__ constexpr int pair_stages(int, bool) { return 6; }
+__host__ __device__ constexpr int pair_stages(int pbn) { return pbn == 256 ? 6 : 8; }
 __host__ __device__ constexpr int pair_red_bytes(int epi, bool out_f32) {
   return pair_stages_out(epi, out_f32) ? EPI_WARPS * P_RED_BYTES : 0;
 }
-constexpr int P_TMEM_COLS = 512;     // two accumulators of 256 columns
 constexpr int P_THREADS = 64 + 32 * EPI_WARPS;
-__host__ __device__ constexpr int pair_smem_bytes(int epi, bool out_f32) {
-  return pair_stages(epi, out_f32) * P_STAGE_BYTES + pair_red_bytes(epi, out_f32) + 256 + 1024;
+__host__ __device__ constexpr int pair_smem_bytes(int epi, bool out_f32, int pbn) {
+  return pair_stages(pbn) * pair_stage_bytes(pbn) + pair_red_bytes(epi, out_f32) + 256 + 1024;
 }
 
-template <int EPI, bool OUT_F32, bool FP8>
+// One problem of a (possibly grouped) launch
+struct PairProblem {
+  CUtensorMap tmA, tmW, tmR;  // tmR: fp32 residual (gate + residual) or bf16 output (TMA store)
+  GemmArgs g;
+};
+
+template <int EPI, bool OUT_F32, bool FP8, int PBN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
-gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
-                         const __grid_constant__ CUtensorMap tmW,
-                         const __grid_constant__ CUtensorMap tmR,  // fp32 residual, gate + residual epilogue only
-                         const GemmArgs g) {
+gemm_pair_tcgen05_kernel(const __grid_constant__ PairProblem p0, const __grid_constant__ PairProblem p1,
+                         const int tiles0, const int tiles1) {
   // M = 256 across the pair; operands bf16, or e4m3 (128 K-elements per 128-byte stage row,
   // 32 per instruction: the byte arithmetic of the stages is the same)
-  constexpr uint32_t IDESC = FP8 ? make_idesc(0, 0, 2 * P_BM, P_BN, 0, 0) : make_idesc(1, 1, 2 * P_BM, P_BN, 0, 0);
+  constexpr uint32_t IDESC = FP8 ? make_idesc(0, 0, 2 * P_BM, PBN, 0, 0) : make_idesc(1, 1, 2 * P_BM, PBN, 0, 0);
+  constexpr int P_BN_HALF = PBN / 2;
+  constexpr int P_STAGE_BYTES = pair_stage_bytes(PBN);
+  constexpr int P_TMEM_COLS = 2 * PBN;  // two accumulators
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  constexpr int P_STAGES = pair_stages(EPI, OUT_F32);
-  uint8_t* red_smem = smem + P_STAGES * P_STAGE_BYTES;  // 1024-byte aligned: stages are 32 KiB each
+  constexpr int P_STAGES = pair_stages(PBN);
+  uint8_t* red_smem = smem + P_STAGES * P_STAGE_BYTES;  // 1024-byte aligned: stages are 32 / 24 KiB each
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + P_STAGES * P_STAGE_BYTES + pair_red_bytes(EPI, OUT_F32));
   uint64_t* empty_bar = full_bar + P_STAGES;
   uint64_t* tfull_bar = empty_bar + P_STAGES;
@@ -98,8 +108,12 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     }
     *s_abort = 0;
     fence_barrier_init();
-    prefetch_tmap(&tmA);
-    prefetch_tmap(&tmW);
+    prefetch_tmap(&p0.tmA);
+    prefetch_tmap(&p0.tmW);
+    if (tiles1 > 0) {
+      prefetch_tmap(&p1.tmA);
+      prefetch_tmap(&p1.tmW);
+    }
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, P_TMEM_COLS);
@@ -110,11 +124,11 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   cluster_sync_all();  // both CTAs' barriers are initialised before any remote signal
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const WaitCtx wc{s_abort, g.status};
+  const WaitCtx wc{s_abort, p0.g.status};
 
-  const int num_tiles = g.tiles_m * g.tiles_n;  // tiles of 256 x 256
-  const int KB = g.k_blocks;
-  constexpr int NSLOT = P_STAGES / 2;  // slots of two stages
+  const int num_tiles = tiles0 + tiles1;  // tiles of 256 x PBN: the first problem's, then the second's
+  constexpr int NSLOT = P_STAGES / 2;     // slots of two stages
+  const int KB = p0.g.k_blocks;        // the same K for both problems
   const int KS = (KB + 1) / 2;         // slots per tile (the last may hold one stage)
 
   if (warp == 0 && lane == 0) {
@@ -123,8 +137,11 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     uint32_t phase = 0;
     bool ok = true;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-      const int m0 = (tile / g.tiles_n) * (2 * P_BM) + static_cast<int>(rank) * P_BM;
-      const int n0 = (tile % g.tiles_n) * P_BN + static_cast<int>(rank) * P_BN_HALF;
+      const bool second = tile >= tiles0;
+      const PairProblem& pp = second ? p1 : p0;
+      const int lt = second ? tile - tiles0 : tile;
+      const int m0 = (lt / pp.g.tiles_n) * (2 * P_BM) + static_cast<int>(rank) * P_BM;
+      const int n0 = (lt % pp.g.tiles_n) * PBN + static_cast<int>(rank) * P_BN_HALF;
       for (int ks = 0; ks < KS; ++ks) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1, wc, DEV_TIMEOUT_EMPTY)) { ok = false; break; }
         {
@@ -135,8 +152,8 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           constexpr int KEL = FP8 ? P_KBYTES : P_KBYTES / 2;  // K elements per stage
           for (int hs = 0; hs < nk; ++hs) {
             uint8_t* sa = smem + (2 * stage + hs) * P_STAGE_BYTES;
-            tma_load_2d_pair(sa, &tmA, bar, (2 * ks + hs) * KEL, m0);
-            tma_load_2d_pair(sa + P_A_BYTES, &tmW, bar, (2 * ks + hs) * KEL, n0);
+            tma_load_2d_pair(sa, &pp.tmA, bar, (2 * ks + hs) * KEL, m0);
+            tma_load_2d_pair(sa + P_A_BYTES, &pp.tmW, bar, (2 * ks + hs) * KEL, n0);
           }
         }
         if (++stage == NSLOT) { stage = 0; phase ^= 1; }
@@ -154,7 +171,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, wc, DEV_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * P_BN);
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * PBN);
         for (int ks = 0; ks < KS; ++ks) {
           // The readiness of this slot was tested while the previous slot's
           // MMAs were being issued; only fall back to a blocking wait if that
@@ -199,18 +216,23 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = pair; tile < num_tiles; tile += num_pairs) {
-      const int m0 = (tile / g.tiles_n) * (2 * P_BM) + static_cast<int>(rank) * P_BM;
-      const int n0 = (tile % g.tiles_n) * P_BN;
+      const bool second = tile >= tiles0;
+      const PairProblem& pp = second ? p1 : p0;
+      const GemmArgs& g = pp.g;
+      const int lt = second ? tile - tiles0 : tile;
+      const int m0 = (lt / g.tiles_n) * (2 * P_BM) + static_cast<int>(rank) * P_BM;
+      const int n0 = (lt % g.tiles_n) * PBN;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
-                             static_cast<uint32_t>(acc * P_BN);
+                             static_cast<uint32_t>(acc * PBN);
       bool drained;
       if constexpr (EPI == EPI_GATE_RESID)
-        drained = drain_tile_gate_reduce<P_BN>(t_row, m0 + quad * 32, n0, half, g, &tmR, &tfull_bar[acc],
-                                               acc_phase, wc, red_smem + (warp - 2) * P_RED_BYTES);
+        drained = drain_tile_gate_reduce<PBN>(t_row, m0 + quad * 32, n0, half, g, &pp.tmR, &tfull_bar[acc],
+                                              acc_phase, wc, red_smem + (warp - 2) * P_RED_BYTES);
       else
-        drained = drain_tile<P_BN, EPI, OUT_F32>(
+        drained = drain_tile<PBN, EPI, OUT_F32>(
             t_row, m0 + row, n0, half, g, &tfull_bar[acc], acc_phase, wc,
-            (pair_stages_out(EPI, OUT_F32) && g.tma_store) ? red_smem + (warp - 2) * P_RED_BYTES : nullptr, &tmR);
+            (pair_stages_out(EPI, OUT_F32) && g.tma_store) ? red_smem + (warp - 2) * P_RED_BYTES : nullptr,
+            &pp.tmR);
       if (!drained) break;
       tc_fence_before_sync();
       __syncwarp();
@@ -234,10 +256,10 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   }
 }
 
-template <int EPI, bool OUT_F32, bool FP8 = false>
-int launch_pair_inst(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmR, const GemmArgs& g,
-                     cudaStream_t stream) {
-  auto kern = gemm_pair_tcgen05_kernel<EPI, OUT_F32, FP8>;
+template <int EPI, bool OUT_F32, bool FP8, int PBN>
+int launch_pair_inst(const PairProblem& p0, const PairProblem& p1, int tiles0, int tiles1, cudaStream_t stream) {
+  auto kern = gemm_pair_tcgen05_kernel<EPI, OUT_F32, FP8, PBN>;
+  constexpr int SMEM = pair_smem_bytes(EPI, OUT_F32, PBN);
   static std::mutex attr_mutex;
   static bool attr_done[64] = {false};
   int dev = 0;
@@ -245,43 +267,47 @@ int launch_pair_inst(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUten
   if (dev >= 0 && dev < 64) {
     std::lock_guard<std::mutex> lock(attr_mutex);
     if (!attr_done[dev]) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_bytes(EPI, OUT_F32));
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
       if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(gemm_pair)");
       attr_done[dev] = true;
     }
   }
-  const int tiles = g.tiles_m * g.tiles_n;
+  const int tiles = tiles0 + tiles1;
   const int max_pairs = device_sm_count() / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
-  kern<<<2 * pairs, P_THREADS, pair_smem_bytes(EPI, OUT_F32), stream>>>(tmA, tmW, tmR, g);
+  kern<<<2 * pairs, P_THREADS, SMEM, stream>>>(p0, p1, tiles0, tiles1);
   return after_launch("gemm_pair_tcgen05_kernel");
 }
 
-}  // namespace
-
-// Whether the CTA-pair kernel covers this problem (bf16 operands, N a multiple
-// of 256, enough rows to fill pair tiles).
-bool gemm_pair_supported(int operand_dtype, int M, int N, int K, const GemmEpilogue& epi) {
-  (void)K;
-  if (N % P_BN != 0 || M < 2 * P_BM) return false;
-  if (epi.mode == EPI_UNPATCHIFY) return false;
-  if (operand_dtype == OPERAND_E4M3) {
-    // e4m3 instantiations exist for the three epilogues of the block GEMMs
-    if (epi.mode == EPI_GATE_RESID) return epi.out_f32 != 0;
-    return (epi.mode == EPI_QKV_NORM || epi.mode == EPI_BIAS_GELU || epi.mode == EPI_BIAS) && !epi.out_f32;
+// the block GEMM epilogues exist for both tile widths, the others for 256 only
+template <int EPI, bool OUT_F32, bool FP8>
+int launch_pair_width(int pbn, const PairProblem& p0, const PairProblem& p1, int tiles0, int tiles1,
+                      cudaStream_t stream) {
+  constexpr bool narrow_built = (EPI == EPI_GATE_RESID && OUT_F32) ||
+                                (!OUT_F32 && (EPI == EPI_BIAS || EPI == EPI_BIAS_GELU || EPI == EPI_QKV_NORM));
+  if constexpr (narrow_built) {
+    if (pbn == 128) return launch_pair_inst<EPI, OUT_F32, FP8, 128>(p0, p1, tiles0, tiles1, stream);
   }
-  return operand_dtype == OPERAND_BF16;
+  return launch_pair_inst<EPI, OUT_F32, FP8, 256>(p0, p1, tiles0, tiles1, stream);
 }
 
-int launch_gemm_pair(const void* A, long lda, const void* W, long ldw, int operand_dtype, int M, int N,
-                     int K, const GemmEpilogue& epi, int* dev_status, cudaStream_t stream) {
+bool narrow_tiles_built(const GemmEpilogue& epi) {
+  if (epi.mode == EPI_GATE_RESID) return epi.out_f32 != 0;
+  return !epi.out_f32 && (epi.mode == EPI_BIAS || epi.mode == EPI_BIAS_GELU || epi.mode == EPI_QKV_NORM);
+}
+
+// Tensor maps and arguments of one problem for pair tiles of width pbn.
+int build_problem(PairProblem* pp, const GemmProblem& q, int operand_dtype, int N, int K, int pbn,
+                  int* dev_status) {
   const bool fp8 = operand_dtype == OPERAND_E4M3;
   const int eb = fp8 ? 1 : 2, kel = P_KBYTES / eb;  // element bytes, K elements per stage
-  GemmArgs g;
+  const GemmEpilogue& epi = q.epi;
+  const int M = q.M;
+  GemmArgs& g = pp->g;
   g.M = M; g.N = N; g.K = K;
   g.k_blocks = (K + kel - 1) / kel;
   g.tiles_m = (M + 2 * P_BM - 1) / (2 * P_BM);
-  g.tiles_n = N / P_BN;
+  g.tiles_n = N / pbn;
   g.epi = epi;
   g.status = dev_status;
   {
@@ -289,19 +315,18 @@ int launch_gemm_pair(const void* A, long lda, const void* W, long ldw, int opera
     g.wide_store = (N % 16 == 0) && ((epi.ldo * esz) % 32 == 0) &&
                    ((reinterpret_cast<uintptr_t>(epi.out) & 31) == 0);
   }
-  CUtensorMap tmA, tmW;
-  int rc = encode_tmap_2d(&tmA, A, eb, (uint64_t)K, (uint64_t)M, (uint64_t)lda * eb, kel, P_BM);
+  int rc = encode_tmap_2d(&pp->tmA, q.A, eb, (uint64_t)K, (uint64_t)M, (uint64_t)q.lda * eb, kel, P_BM);
   if (rc) return rc;
-  rc = encode_tmap_2d(&tmW, W, eb, (uint64_t)K, (uint64_t)N, (uint64_t)ldw * eb, kel, P_BN_HALF);
+  rc = encode_tmap_2d(&pp->tmW, q.W, eb, (uint64_t)K, (uint64_t)N, (uint64_t)q.ldw * eb, kel, pbn / 2);
   if (rc) return rc;
   const bool f32 = epi.out_f32 != 0;
-  CUtensorMap tmR = tmA;  // placeholder for the epilogues that do not reduce
+  pp->tmR = pp->tmA;  // placeholder for the epilogues that neither reduce nor store through TMA
   if (epi.mode == EPI_GATE_RESID) {
     if (epi.out != epi.resid) {
       set_last_error("gemm_pair: gate/residual epilogue updates the residual in place (out must equal resid)");
       return ST_INVALID_ARG;
     }
-    rc = encode_tmap_2d(&tmR, epi.resid, 4, (uint64_t)N, (uint64_t)M, (uint64_t)epi.ldo * 4, 32, 32);
+    rc = encode_tmap_2d(&pp->tmR, epi.resid, 4, (uint64_t)N, (uint64_t)M, (uint64_t)epi.ldo * 4, 32, 32);
     if (rc) return rc;
   }
   // bf16 outputs leave through a TMA store when every warp's 32 rows are 32 consecutive
@@ -310,47 +335,97 @@ int launch_gemm_pair(const void* A, long lda, const void* W, long ldw, int opera
   if (!f32 && !epi.out_e4m3 && M % 32 == 0 && (epi.rows_in == 0 || epi.rows_in % 32 == 0) &&
       (epi.mode == EPI_BIAS || epi.mode == EPI_BIAS_GELU || epi.mode == EPI_QKV_NORM) &&
       (epi.ldo * 2) % 16 == 0 && (reinterpret_cast<uintptr_t>(epi.out) & 15) == 0) {
-    const uint64_t out_rows =
-        epi.rows_in > 0 ? (uint64_t)(M / epi.rows_in) * epi.rows_out + 0 : (uint64_t)M;
     // with a row remap the last sample's rows end at (samples - 1) * rows_out + row_off + rows_in
     const uint64_t extent = epi.rows_in > 0
                                 ? (uint64_t)(M / epi.rows_in - 1) * epi.rows_out + epi.row_off + epi.rows_in
-                                : out_rows;
-    rc = encode_tmap_2d(&tmR, epi.out, 2, (uint64_t)N, extent, (uint64_t)epi.ldo * 2, 64, 32);
+                                : (uint64_t)M;
+    rc = encode_tmap_2d(&pp->tmR, epi.out, 2, (uint64_t)N, extent, (uint64_t)epi.ldo * 2, 64, 32);
     if (rc) return rc;
     g.tma_store = 1;
   }
+  return ST_OK;
+}
+
+// 256-wide tiles unless they would leave much of the last wave empty and 128-wide ones would not
+// (the narrow tile moves a third more operand bytes per FLOP, so it has to win clearly).
+int choose_tile_width(long tiles256, const GemmEpilogue& epi) {
+  if (!narrow_tiles_built(epi)) return 256;
+  const long pairs = device_sm_count() / 2;
+  if (pairs <= 0 || tiles256 >= 6 * pairs) return 256;
+  auto fill = [&](long tiles) { return static_cast<double>(tiles) / static_cast<double>(((tiles + pairs - 1) / pairs) * pairs); };
+  return 0.92 * fill(2 * tiles256) > fill(tiles256) + 0.03 ? 128 : 256;
+}
+
+}  // namespace
+
+// Whether the CTA-pair kernel covers this problem (N a multiple of 256, enough rows to fill
+// pair tiles, an epilogue that is instantiated for the operand type).
+bool gemm_pair_supported(int operand_dtype, int M, int N, int K, const GemmEpilogue& epi) {
+  (void)K;
+  if (N % 256 != 0 || M < 2 * P_BM) return false;
+  if (epi.mode == EPI_UNPATCHIFY) return false;
+  if (operand_dtype == OPERAND_E4M3) {
+    // e4m3 instantiations exist for the epilogues of the block GEMMs
+    if (epi.mode == EPI_GATE_RESID) return epi.out_f32 != 0;
+    return (epi.mode == EPI_QKV_NORM || epi.mode == EPI_BIAS_GELU || epi.mode == EPI_BIAS) && !epi.out_f32;
+  }
+  return operand_dtype == OPERAND_BF16;
+}
+
+// One or two problems (b may be null) of the same N, K, operand type and epilogue kind.
+int launch_gemm_pair(const GemmProblem& a, const GemmProblem* b, int operand_dtype, int N, int K,
+                     int* dev_status, cudaStream_t stream) {
+  const bool fp8 = operand_dtype == OPERAND_E4M3;
+  if (b && (b->epi.mode != a.epi.mode || b->epi.out_f32 != a.epi.out_f32)) {
+    set_last_error("gemm_pair: grouped problems need the same epilogue kind");
+    return ST_INVALID_ARG;
+  }
+  const long tiles256 = static_cast<long>((a.M + 255) / 256 + (b ? (b->M + 255) / 256 : 0)) * (N / 256);
+  const int pbn = choose_tile_width(tiles256, a.epi);
+  PairProblem p0, p1;
+  int rc = build_problem(&p0, a, operand_dtype, N, K, pbn, dev_status);
+  if (rc) return rc;
+  int tiles1 = 0;
+  if (b) {
+    rc = build_problem(&p1, *b, operand_dtype, N, K, pbn, dev_status);
+    if (rc) return rc;
+    tiles1 = p1.g.tiles_m * p1.g.tiles_n;
+  } else {
+    p1 = p0;
+  }
+  const int tiles0 = p0.g.tiles_m * p0.g.tiles_n;
+  const bool f32 = a.epi.out_f32 != 0;
   if (fp8) {
-    switch (epi.mode) {
-      case EPI_BIAS: return launch_pair_inst<EPI_BIAS, false, true>(tmA, tmW, tmR, g, stream);
-      case EPI_BIAS_GELU: return launch_pair_inst<EPI_BIAS_GELU, false, true>(tmA, tmW, tmR, g, stream);
-      case EPI_QKV_NORM: return launch_pair_inst<EPI_QKV_NORM, false, true>(tmA, tmW, tmR, g, stream);
-      case EPI_GATE_RESID: return launch_pair_inst<EPI_GATE_RESID, true, true>(tmA, tmW, tmR, g, stream);
+    switch (a.epi.mode) {
+      case EPI_BIAS: return launch_pair_width<EPI_BIAS, false, true>(pbn, p0, p1, tiles0, tiles1, stream);
+      case EPI_BIAS_GELU: return launch_pair_width<EPI_BIAS_GELU, false, true>(pbn, p0, p1, tiles0, tiles1, stream);
+      case EPI_QKV_NORM: return launch_pair_width<EPI_QKV_NORM, false, true>(pbn, p0, p1, tiles0, tiles1, stream);
+      case EPI_GATE_RESID: return launch_pair_width<EPI_GATE_RESID, true, true>(pbn, p0, p1, tiles0, tiles1, stream);
       default: break;
     }
-    set_last_error("gemm_pair: no e4m3 instantiation for epilogue mode %d", epi.mode);
+    set_last_error("gemm_pair: no e4m3 instantiation for epilogue mode %d", a.epi.mode);
     return ST_UNSUPPORTED;
   }
-  switch (epi.mode) {
+  switch (a.epi.mode) {
     case EPI_BIAS:
-      return f32 ? launch_pair_inst<EPI_BIAS, true>(tmA, tmW, tmR, g, stream)
-                 : launch_pair_inst<EPI_BIAS, false>(tmA, tmW, tmR, g, stream);
+      return f32 ? launch_pair_width<EPI_BIAS, true, false>(pbn, p0, p1, tiles0, tiles1, stream)
+                 : launch_pair_width<EPI_BIAS, false, false>(pbn, p0, p1, tiles0, tiles1, stream);
     case EPI_BIAS_GELU:
-      return f32 ? launch_pair_inst<EPI_BIAS_GELU, true>(tmA, tmW, tmR, g, stream)
-                 : launch_pair_inst<EPI_BIAS_GELU, false>(tmA, tmW, tmR, g, stream);
+      return f32 ? launch_pair_width<EPI_BIAS_GELU, true, false>(pbn, p0, p1, tiles0, tiles1, stream)
+                 : launch_pair_width<EPI_BIAS_GELU, false, false>(pbn, p0, p1, tiles0, tiles1, stream);
     case EPI_GATE_RESID:
       if (!f32) break;
-      return launch_pair_inst<EPI_GATE_RESID, true>(tmA, tmW, tmR, g, stream);
+      return launch_pair_width<EPI_GATE_RESID, true, false>(pbn, p0, p1, tiles0, tiles1, stream);
     case EPI_QKV_NORM:
-      return f32 ? launch_pair_inst<EPI_QKV_NORM, true>(tmA, tmW, tmR, g, stream)
-                 : launch_pair_inst<EPI_QKV_NORM, false>(tmA, tmW, tmR, g, stream);
+      return f32 ? launch_pair_width<EPI_QKV_NORM, true, false>(pbn, p0, p1, tiles0, tiles1, stream)
+                 : launch_pair_width<EPI_QKV_NORM, false, false>(pbn, p0, p1, tiles0, tiles1, stream);
     case EPI_ADD_TABLE:
       if (!f32) break;
-      return launch_pair_inst<EPI_ADD_TABLE, true>(tmA, tmW, tmR, g, stream);
+      return launch_pair_width<EPI_ADD_TABLE, true, false>(pbn, p0, p1, tiles0, tiles1, stream);
     default:
       break;
   }
-  set_last_error("gemm_pair: unsupported epilogue mode %d / out_f32 %d", epi.mode, epi.out_f32);
+  set_last_error("gemm_pair: unsupported epilogue mode %d / out_f32 %d", a.epi.mode, a.epi.out_f32);
   return ST_UNSUPPORTED;
 }
 

@@ -339,11 +339,13 @@ int dispatch_epi(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmArgs&
 }  // namespace
 
 bool gemm_pair_supported(int operand_dtype, int M, int N, int K, const GemmEpilogue& epi);
-int launch_gemm_pair(const void* A, long lda, const void* W, long ldw, int operand_dtype, int M, int N,
-                     int K, const GemmEpilogue& epi, int* dev_status, cudaStream_t stream);
+int launch_gemm_pair(const GemmProblem& a, const GemmProblem* b, int operand_dtype, int N, int K,
+                     int* dev_status, cudaStream_t stream);
 
-int launch_gemm(const void* A, long lda, const void* W, long ldw, int operand_dtype, int M, int N,
-                int K, const GemmEpilogue& epi, int* dev_status, cudaStream_t stream) {
+namespace {
+// argument checks shared by the single and the grouped launch
+int validate_gemm(const void* A, long lda, const void* W, long ldw, int operand_dtype, int M, int N, int K,
+                  const GemmEpilogue& epi) {
   if (M <= 0 || N <= 0 || K <= 0 || !A || !W || !epi.out) {
     set_last_error("gemm: invalid argument (M %d N %d K %d)", M, N, K);
     return ST_INVALID_ARG;
@@ -384,9 +386,35 @@ int launch_gemm(const void* A, long lda, const void* W, long ldw, int operand_dt
     set_last_error("gemm: table epilogue needs table and rows_in");
     return ST_INVALID_ARG;
   }
-  // Large problems go to the CTA-pair kernel (256 x 256 tiles across two SMs).
-  if (gemm_pair_supported(operand_dtype, M, N, K, epi))
-    return launch_gemm_pair(A, lda, W, ldw, operand_dtype, M, N, K, epi, dev_status, stream);
+  return ST_OK;
+}
+}  // namespace
+
+int launch_gemm_grouped(const GemmProblem& a, const GemmProblem& b, int operand_dtype, int N, int K,
+                        int* dev_status, cudaStream_t stream) {
+  int rc = validate_gemm(a.A, a.lda, a.W, a.ldw, operand_dtype, a.M, N, K, a.epi);
+  if (rc) return rc;
+  rc = validate_gemm(b.A, b.lda, b.W, b.ldw, operand_dtype, b.M, N, K, b.epi);
+  if (rc) return rc;
+  if (a.epi.mode == b.epi.mode && a.epi.out_f32 == b.epi.out_f32 &&
+      gemm_pair_supported(operand_dtype, a.M, N, K, a.epi) && gemm_pair_supported(operand_dtype, b.M, N, K, b.epi))
+    return launch_gemm_pair(a, &b, operand_dtype, N, K, dev_status, stream);
+  rc = launch_gemm(a.A, a.lda, a.W, a.ldw, operand_dtype, a.M, N, K, a.epi, dev_status, stream);
+  if (rc) return rc;
+  return launch_gemm(b.A, b.lda, b.W, b.ldw, operand_dtype, b.M, N, K, b.epi, dev_status, stream);
+}
+
+int launch_gemm(const void* A, long lda, const void* W, long ldw, int operand_dtype, int M, int N,
+                int K, const GemmEpilogue& epi, int* dev_status, cudaStream_t stream) {
+  int rcv = validate_gemm(A, lda, W, ldw, operand_dtype, M, N, K, epi);
+  if (rcv) return rcv;
+  const int eb = operand_dtype == OPERAND_E4M3 ? 1 : 2;
+  // Large problems go to the CTA-pair kernel (256-row tiles across two SMs).
+  if (gemm_pair_supported(operand_dtype, M, N, K, epi)) {
+    GemmProblem q;
+    q.A = A; q.lda = lda; q.W = W; q.ldw = ldw; q.M = M; q.epi = epi;
+    return launch_gemm_pair(q, nullptr, operand_dtype, N, K, dev_status, stream);
+  }
 
   const int BN = (N >= 256 && N % 256 == 0) ? 256 : (N > 64 ? 128 : 64);
   const int elems_per_stage = STAGE_K_BYTES / eb;

@@ -79,6 +79,21 @@ enum : int { OPERAND_BF16 = 0, OPERAND_E4M3 = 1 };
 int launch_gemm(const void* A, long lda, const void* W, long ldw, int operand_dtype, int M, int N,
                 int K, const GemmEpilogue& epi, int* dev_status, cudaStream_t stream);
 
+// One operand set of a grouped launch: acc = A (M x K) * W^T (N x K), then epi.
+struct GemmProblem {
+  const void* A = nullptr;
+  long lda = 0;
+  const void* W = nullptr;
+  long ldw = 0;
+  int M = 0;
+  GemmEpilogue epi;
+};
+// Two GEMMs of the same N, K, operand type and epilogue kind as ONE launch when the CTA-pair
+// kernel covers both (the second problem's tiles run in the tail of the first's); otherwise
+// two launches.  Used for the image-stream GEMM of a block and its small context-stream twin.
+int launch_gemm_grouped(const GemmProblem& a, const GemmProblem& b, int operand_dtype, int N, int K,
+                        int* dev_status, cudaStream_t stream);
+
 // ----------------------------------------------------------------------------
 // Flash-style attention on tcgen05 (head_dim 64, bf16, non-causal).
 // qkv: (B, T, 3*E) bf16 with q | k | v column blocks, head h at columns h*64.

@@ -32,7 +32,7 @@ def test_bench_line_of_this_arm():
     assert "workload" in d["config"] and "model" not in d["config"] and d["config"]["per_gpu_batch"] == 8
     assert abs(d["weak_value"] - d["value"]) < 1e-9  # one GPU: the two readings coincide
     assert abs(d["value"] * d["ms_per_step"] - 1000.0) < 1e-6 * 1000.0
-    assert d["gpu_launches"] >= 2 * 300  # ~360 kernels per step
+    assert d["gpu_launches"] >= 2 * 250  # ~267 kernels per step
     e = d["e2e"]
     assert e["unit"] == "steps/s" and 0 < e["value"] <= 1.05 * d["value"]
     assert e["h2d_bytes_per_step"] == (8 * 16 * 128 * 128 + 8 * 333 * 4096 + 8 * 2048) * 2 + 8 * 4
