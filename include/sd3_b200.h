@@ -111,6 +111,19 @@ SD3_API int sd3_qkv_project(const void* x_bf16, const void* w_nk_bf16, const flo
                     const float* wk, float eps, void* qkv_out_bf16, int B, int T_in, int T_total,
                     int row_offset, int E, void* stream);
 
+/* QKV projection for sequence-parallel attention: out = per-head RMSNorm(x W^T + b) as in
+ * sd3_qkv_project, for `rows` rows with K input features and q|k|v blocks of E_out columns
+ * each (head_dim 64), written in head-group layout (head_groups, rows, 3, E_out/head_groups):
+ * slab g holds the q, k and v columns of the heads of group g for every row, which is the
+ * send buffer of the all-to-all that turns "my tokens x all heads" into "all tokens x my
+ * heads" (head_groups = 1 gives the plain (rows, 3 E_out) layout).  K may differ from E_out,
+ * so the same call projects replicated rows onto one rank's heads with a sliced weight.
+ * Math: latent_to_qkv / context_to_qkv + RMSNorm, module_tests/modules.py:272-297; the
+ * reference has no distributed path. */
+SD3_API int sd3_qkv_project_groups(const void* x_bf16, const void* w_nk_bf16, const float* bias,
+                                   const float* wq, const float* wk, float eps, void* out_bf16, int rows,
+                                   int E_out, int K, int head_groups, void* stream);
+
 /* Non-causal multi-head attention, head_dim 64, over the packed qkv buffer
  * (B, T, 3E) bf16.  Rows t < Tc of each sample are written to out_c (B, Tc, E)
  * (skipped when NULL), the others to out_x (B, T - Tc, E); both bf16.

@@ -175,6 +175,33 @@ int sd3_qkv_project(const void* x, const void* w, const float* bias, const float
                      S(stream));
 }
 
+int sd3_qkv_project_groups(const void* x, const void* w, const float* bias, const float* wq,
+                           const float* wk, float eps, void* out, int rows, int E_out, int K, int head_groups,
+                           void* stream) {
+  if (rows <= 0 || E_out <= 0 || K <= 0 || head_groups < 1 || E_out % (64 * head_groups) || K % 8) {
+    set_last_error("sd3_qkv_project_groups: invalid shape (rows %d E_out %d K %d groups %d)", rows, E_out, K,
+                   head_groups);
+    return SD3_ERR_INVALID_ARG;
+  }
+  GemmEpilogue e;
+  e.mode = EPI_QKV_NORM;
+  e.bias = bias;
+  e.out = out;
+  e.out_f32 = 0;
+  e.ldo = 3L * E_out;
+  e.rows_in = rows;
+  e.rows_out = rows;
+  e.row_off = 0;
+  e.wq = wq;
+  e.wk = wk;
+  e.qk_cols = 2 * E_out;
+  e.eps = eps;
+  e.do_norm = (wq || wk) ? 1 : 0;
+  e.hg_groups = head_groups;
+  e.hg_rows = rows;
+  return launch_gemm(x, K, w, K, OPERAND_BF16, rows, 3 * E_out, K, e, device_status_word(), S(stream));
+}
+
 int sd3_attention(const void* qkv, int B, int T, int num_heads, int Tc, void* out_c, void* out_x,
                   float scale, void* stream) {
   return launch_attention_bf16(static_cast<const bf16*>(qkv), B, T, num_heads, Tc,

@@ -333,7 +333,7 @@ int build_problem(PairProblem* pp, const GemmProblem& q, int operand_dtype, int 
   // output rows that all exist
   g.tma_store = 0;
   if (!f32 && !epi.out_e4m3 && M % 32 == 0 && (epi.rows_in == 0 || epi.rows_in % 32 == 0) &&
-      (epi.mode == EPI_BIAS || epi.mode == EPI_BIAS_GELU || epi.mode == EPI_QKV_NORM) &&
+      (epi.mode == EPI_BIAS || epi.mode == EPI_BIAS_GELU || epi.mode == EPI_QKV_NORM) && epi.hg_groups <= 1 &&
       (epi.ldo * 2) % 16 == 0 && (reinterpret_cast<uintptr_t>(epi.out) & 15) == 0) {
     // with a row remap the last sample's rows end at (samples - 1) * rows_out + row_off + rows_in
     const uint64_t extent = epi.rows_in > 0

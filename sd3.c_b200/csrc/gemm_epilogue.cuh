@@ -217,10 +217,17 @@ __device__ __forceinline__ void epilogue_64(float (&v)[64], const RowMap& rm, in
       return;
     }
   }
-  const long base = rm.orow * e.ldo;
+  long base = rm.orow * e.ldo + n_base;  // element offset of this thread's 64 values
+  if constexpr (EPI == EPI_QKV_NORM) {
+    if (e.hg_groups > 1) {  // head-group layout: a 64-column chunk is one head and stays contiguous
+      const int Eo = e.qk_cols >> 1, Eh = Eo / e.hg_groups;
+      const int part = n_base / Eo, e0 = n_base - part * Eo, grp = e0 / Eh;
+      base = (static_cast<long>(grp) * e.hg_rows + rm.orow) * (3L * Eh) + part * Eh + (e0 - grp * Eh);
+    }
+  }
   if constexpr (!OUT_F32 && (EPI == EPI_BIAS || EPI == EPI_BIAS_GELU)) {
     if (e.out_e4m3) {  // 64 bytes per thread; N % 64 == 0 is checked at launch
-      uint4* q = reinterpret_cast<uint4*>(static_cast<uint8_t*>(e.out) + base + n_base);
+      uint4* q = reinterpret_cast<uint4*>(static_cast<uint8_t*>(e.out) + base);
 #pragma unroll
       for (int gi = 0; gi < 4; ++gi) {
         const float* o = &v[gi * 16];
@@ -233,12 +240,12 @@ __device__ __forceinline__ void epilogue_64(float (&v)[64], const RowMap& rm, in
   if (n_base + 64 <= N) {
 #pragma unroll
     for (int gi = 0; gi < 4; ++gi)
-      store16<OUT_F32>(e.out, base + n_base + gi * 16, &v[gi * 16], g.wide_store != 0);
+      store16<OUT_F32>(e.out, base + gi * 16, &v[gi * 16], g.wide_store != 0);
   } else {
 #pragma unroll
     for (int gi = 0; gi < 8; ++gi) {
       const int n = n_base + gi * 8;
-      if (n < N) store8<OUT_F32>(e.out, base + n, &v[gi * 8]);
+      if (n < N) store8<OUT_F32>(e.out, base + gi * 8, &v[gi * 8]);
     }
   }
 }

@@ -62,6 +62,11 @@ struct GemmEpilogue {
   int qk_cols = 0;
   float eps = 1e-6f;
   int do_norm = 1;
+  // EPI_QKV_NORM, optional head-group layout (hg_groups > 1): the output is
+  // (hg_groups, hg_rows, 3, E / hg_groups) -- slab g holds the q, k and v columns of the heads
+  // of group g for every row -- instead of (rows, 3E); the send layout of a head all-to-all.
+  int hg_groups = 0;
+  long hg_rows = 0;
   // EPI_ADD_TABLE
   const float* table = nullptr;  // (rows_in, N) fp32
   // EPI_UNPATCHIFY

@@ -62,6 +62,7 @@ PROTOTYPES = {
     "sd3_quantize_e4m3": (c_int, [c_void_p, c_int, c_void_p, c_long, c_float, c_void_p]),
     "sd3_linear_gate_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
     "sd3_qkv_project": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "sd3_qkv_project_groups": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "sd3_attention": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p]),
     "sd3_attention_generic": (c_int, [c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_long, c_int, c_float, c_void_p]),
     "sd3_layernorm_modulate": (c_int, [c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p]),
@@ -207,6 +208,14 @@ def qkv_project(x_bf16, w_nk_bf16, bias, wq, wk, eps, qkv_out, B, T_in, T_total,
                                 ptr(qkv_out), B, T_in, T_total, row_offset, E, stream_ptr()),
           "sd3_qkv_project")
     return qkv_out
+
+
+def qkv_project_groups(x_bf16, w_nk_bf16, bias, wq, wk, eps, out, E_out, head_groups):
+    """out (head_groups, rows, 3, E_out/head_groups) bf16: see sd3_qkv_project_groups."""
+    rows, K = x_bf16.shape
+    check(lib().sd3_qkv_project_groups(ptr(x_bf16), ptr(w_nk_bf16), ptr(bias), ptr(wq), ptr(wk), eps, ptr(out),
+                                       rows, E_out, K, head_groups, stream_ptr()), "sd3_qkv_project_groups")
+    return out
 
 
 def attention(qkv_bf16, B, T, num_heads, Tc, scale, want_context=True):

@@ -80,13 +80,47 @@ class DistComm:
         self.dist.all_gather_into_tensor(out, t.contiguous(), group=self.group)
         return out
 
+    # variants into preallocated (contiguous) outputs: chunk d of `send` goes to rank d,
+    # chunk s of `out` comes from rank s
+    def all_to_all_into(self, out, send):
+        self.dist.all_to_all_single(out.reshape(-1), send.reshape(-1), group=self.group)
+
+    def all_gather_into(self, out, t):
+        self.dist.all_gather_into_tensor(out.reshape(-1), t.reshape(-1), group=self.group)
+
+
+class LocalComm:
+    """The one-rank communicator: every exchange is a copy.  Lets the sharded forward run
+    (and be tested) on a single GPU without a process group."""
+    rank = 0
+    world = 1
+
+    def all_to_all(self, send):
+        return send.clone()
+
+    def all_gather(self, t):
+        return t.unsqueeze(0).clone()
+
+    def all_to_all_into(self, out, send):
+        out.reshape(-1).copy_(send.reshape(-1))
+
+    def all_gather_into(self, out, t):
+        out.reshape(-1).copy_(t.reshape(-1))
+
 
 # ---------------------------------------------------------------------------
 # packed weights of one model, kept as torch tensors (device memory plumbing)
 # ---------------------------------------------------------------------------
 class PackedModel:
     """bf16 packed (out, in) weights for the op-level ABI, from the reference
-    params dict (2-D weights (in, out); module_tests/DiT.py:25-31)."""
+    params dict (2-D weights (in, out); module_tests/DiT.py:25-31).
+
+    Two things are prepared once per model so that the forward needs no glue:
+    the AdaLN matrices of all blocks and of the final layer are concatenated
+    (one GEMM with M = 1 yields every modulation vector of the step), and, once
+    the rank is known (`for_rank`), the context QKV weights are sliced to the
+    heads this rank owns (the context rows are replicated, so each rank projects
+    them onto its own heads only)."""
 
     def __init__(self, sd3, params, cfg):
         torch = _torch()
@@ -101,10 +135,62 @@ class PackedModel:
                 self.w[name] = t.reshape(t.shape[0], -1).to(torch.bfloat16).contiguous()
             else:
                 self.w[name] = t.to(torch.float32).contiguous()
+        # all AdaLN vectors of the step from one GEMM: rows [off, off + n) per (layer, stream)
+        L = cfg["num_layers"]
+        ws, bs, self.ada_off, off = [], [], {}, 0
+        names = []
+        for l in range(L):
+            names += ["transformer.%d.context_ada_lnorm.linear" % l, "transformer.%d.latent_ada_lnorm.linear" % l]
+        names.append("ada_ln_out.linear")
+        for n in names:
+            w, b = self.w.pop(n + ".weight"), self.w.pop(n + ".bias")
+            self.ada_off[n] = (off, w.shape[0])
+            off += w.shape[0]
+            ws.append(w)
+            bs.append(b)
+        self.ada_w = torch.cat(ws, 0).contiguous()
+        self.ada_b = torch.cat(bs, 0).contiguous()
+        self.ada_total = off
+        self.local = None
+        self.ws = {}
         torch.cuda.synchronize()
 
     def lin(self, name):
         return self.w[name + ".weight"], self.w[name + ".bias"]
+
+    def for_rank(self, rank, P):
+        """Context QKV weights restricted to the heads of `rank` (q, k and v rows of that
+        head group), as (3 E/P, E) matrices."""
+        if self.local is not None and self.local[0] == (rank, P):
+            return self.local[1]
+        torch = _torch()
+        E = self.cfg["emb_dim"]
+        Eh = E // P
+        out = {}
+        for l in range(self.cfg["num_layers"]):
+            w, b = self.lin("transformer.%d.context_to_qkv" % l)
+            rows = torch.cat([torch.arange(part * E + rank * Eh, part * E + (rank + 1) * Eh) for part in range(3)]).to(w.device)
+            out[l] = (w.index_select(0, rows).contiguous(), b.index_select(0, rows).contiguous())
+        self.local = ((rank, P), out)
+        return out
+
+    def buffers(self, Tc, Tl, P, dual_any):
+        """Activation buffers of the sharded forward, allocated once per shape."""
+        key = (Tc, Tl, P)
+        if key in self.ws:
+            return self.ws[key]
+        torch = _torch()
+        E = self.cfg["emb_dim"]
+        F = E * self.cfg["mlp_expand"]
+        Eh = E // P
+        bf, dev = torch.bfloat16, "cuda"
+        e = lambda *shape: torch.empty(shape, device=dev, dtype=bf)
+        b = dict(h_c=e(Tc, E), h_x=e(Tl, E), h_x2=e(Tl, E), send=e(P, Tl, 3, Eh), att_in=e(1, Tc + P * Tl, 3 * Eh),
+                 att2=e(1, P * Tl, 3 * Eh), o_c=e(1, Tc, Eh), o_x=e(1, P * Tl, Eh), recv_o=e(P, Tl, Eh),
+                 o_rows=e(Tl, E), gath_c=e(P, Tc, Eh), o_ctx=e(Tc, E), hid_x=e(Tl, F), hid_c=e(Tc, F),
+                 mod=torch.empty((1, self.ada_total), device=dev, dtype=torch.float32))
+        self.ws[key] = b
+        return b
 
 
 def _gate_resid(sd3, x_bf16, w, b, gate_row, resid):
@@ -114,14 +200,38 @@ def _gate_resid(sd3, x_bf16, w, b, gate_row, resid):
         x_bf16.shape[0], w.shape[0], x_bf16.shape[1], sd3.stream_ptr()), "sd3_linear_gate_residual")
 
 
-def _ln_mod(sd3, x, E, eps, shift, scale, shift2=None, scale2=None):
-    return sd3.layernorm_modulate(x, 1, x.shape[0], E, eps, shift, scale, shift2, scale2, mod_stride=0)
+def _ln_mod(sd3, x, E, eps, shift, scale, out1, shift2=None, scale2=None, out2=None):
+    """LayerNorm + modulate of (rows, E) f32 rows of one sample into preallocated bf16 outputs."""
+    from ctypes import c_void_p
+    sd3.check(sd3.lib().sd3_layernorm_modulate(
+        sd3.ptr(x), 1, x.shape[0], E, eps, c_void_p(shift.data_ptr()), c_void_p(scale.data_ptr()), sd3.ptr(out1),
+        c_void_p(shift2.data_ptr()) if shift2 is not None else None,
+        c_void_p(scale2.data_ptr()) if scale2 is not None else None,
+        sd3.ptr(out2) if shift2 is not None else None, 0, sd3.DTYPE_BF16, sd3.stream_ptr()), "sd3_layernorm_modulate")
 
 
-def block_forward(pm, l, y, c, x_loc, comm, last, dual):
+def _linear_into(sd3, x, w, b, out, act=0):
+    sd3.check(sd3.lib().sd3_linear(sd3.ptr(x), sd3.ptr(w), sd3.ptr(b), sd3.ptr(out), sd3.dtype_tag(out),
+                                   x.shape[0], w.shape[0], x.shape[1], act, sd3.stream_ptr()), "sd3_linear")
+    return out
+
+
+def _attention_into(sd3, att_in, T, heads, Tc, scale, o_c, o_x):
+    sd3.check(sd3.lib().sd3_attention(sd3.ptr(att_in), 1, T, heads, Tc, sd3.ptr(o_c) if o_c is not None else None,
+                                      sd3.ptr(o_x), scale, sd3.stream_ptr()), "sd3_attention")
+
+
+def block_forward(pm, l, mod, c, x_loc, comm, last, dual):
     """One MMDiT(-X) block with the image rows sharded: c (Tc, E) f32 replicated,
-    x_loc (Tl, E) f32 local rows; both updated in place."""
-    torch = _torch()
+    x_loc (Tl, E) f32 local rows; both updated in place.  mod: the (ada_total,) f32
+    vector of all AdaLN outputs of the step.
+
+    No tensor is re-laid between kernels: the image QKV GEMM writes the all-to-all send
+    buffer (head-group layout) directly, the context rows are projected onto the local
+    heads with a sliced weight straight into the attention input, the all-to-all delivers
+    the image rows behind them in token order, and the attention output is already
+    partitioned by destination rank.  The one copy left per attention turns the returned
+    (source rank, row, head-group columns) slabs into (row, all columns) rows."""
     sd3 = pm.sd3
     cfg = pm.cfg
     E, NH = cfg["emb_dim"], cfg["attn_heads"]
@@ -129,12 +239,14 @@ def block_forward(pm, l, y, c, x_loc, comm, last, dual):
     Eh = E // P
     pre = "transformer.%d." % l
     Tc, Tl = c.shape[0], x_loc.shape[0]
+    Tx = P * Tl
     scale = (E // NH) ** -0.5
+    B = pm.buffers(Tc, Tl, P, True)
+    ctx_local = pm.for_rank(rank, P)
 
-    wa, ba = pm.lin(pre + "context_ada_lnorm.linear")
-    cm = sd3.skinny_linear(y, wa, ba)[0]
-    wa, ba = pm.lin(pre + "latent_ada_lnorm.linear")
-    xm = sd3.skinny_linear(y, wa, ba)[0]
+    oc, nc = pm.ada_off[pre + "context_ada_lnorm.linear"]
+    ox, nx = pm.ada_off[pre + "latent_ada_lnorm.linear"]
+    cm, xm = mod[oc:oc + nc], mod[ox:ox + nx]
     ch = lambda v, i: v[i * E:(i + 1) * E]
     if last:
         c_scale_a, c_shift_a = ch(cm, 0), ch(cm, 1)
@@ -142,57 +254,57 @@ def block_forward(pm, l, y, c, x_loc, comm, last, dual):
         c_shift_a, c_scale_a, c_gate_a, c_shift_m, c_scale_m, c_gate_m = (ch(cm, i) for i in range(6))
     x_shift_a, x_scale_a, x_gate_a, x_shift_m, x_scale_m, x_gate_m = (ch(xm, i) for i in range(6))
 
-    h_c, _ = _ln_mod(sd3, c, E, 1e-6, c_shift_a, c_scale_a)
+    _ln_mod(sd3, c, E, 1e-6, c_shift_a, c_scale_a, B["h_c"])
     if dual:
-        h_x, h_x2 = _ln_mod(sd3, x_loc, E, 1e-6, x_shift_a, x_scale_a, ch(xm, 6), ch(xm, 7))
+        _ln_mod(sd3, x_loc, E, 1e-6, x_shift_a, x_scale_a, B["h_x"], ch(xm, 6), ch(xm, 7), B["h_x2"])
     else:
-        h_x, h_x2 = _ln_mod(sd3, x_loc, E, 1e-6, x_shift_a, x_scale_a)
+        _ln_mod(sd3, x_loc, E, 1e-6, x_shift_a, x_scale_a, B["h_x"])
 
     def rms(n):
         return pm.w.get(pre + n + "_rmsnorm_query.weight"), pm.w.get(pre + n + "_rmsnorm_key.weight")
 
-    # local QKV (context rows first), then tokens x all heads -> all tokens x my heads
-    qkv = torch.empty((1, Tc + Tl, 3 * E), device=c.device, dtype=torch.bfloat16)
-    w, b = pm.lin(pre + "context_to_qkv")
+    # joint attention: context rows (my heads) | image rows of every rank (my heads)
+    att_in = B["att_in"]
+    wl, bl = ctx_local[l]
     wq, wk = rms("context")
-    sd3.qkv_project(h_c, w, b, wq, wk, 1e-6, qkv, 1, Tc, Tc + Tl, 0, E)
+    sd3.qkv_project_groups(B["h_c"], wl, bl, wq, wk, 1e-6, att_in, Eh, 1)  # rows [0, Tc) of att_in
     w, b = pm.lin(pre + "latent_to_qkv")
     wq, wk = rms("latent")
-    sd3.qkv_project(h_x, w, b, wq, wk, 1e-6, qkv, 1, Tl, Tc + Tl, Tc, E)
-    recv = comm.all_to_all(split_heads_for_send(qkv[0, Tc:], P))
-    att_in = assemble_attention_input(qkv[0, :Tc], recv, rank, P)
-    o_c, o_x = sd3.attention(att_in, 1, Tc + P * Tl, NH // P, Tc, scale, want_context=not last)
-    o_rows = assemble_rows(comm.all_to_all(split_tokens_for_send(o_x[0], P)))
+    sd3.qkv_project_groups(B["h_x"], w, b, wq, wk, 1e-6, B["send"], E, P)
+    comm.all_to_all_into(att_in[0, Tc:], B["send"])
+    _attention_into(sd3, att_in, Tc + Tx, NH // P, Tc, scale, None if last else B["o_c"], B["o_x"])
+    comm.all_to_all_into(B["recv_o"], B["o_x"])
+    B["o_rows"].view(Tl, P, Eh).copy_(B["recv_o"].permute(1, 0, 2))
     if not last:
-        o_ctx = assemble_rows(comm.all_gather(o_c[0]))  # (P, Tc, Eh) -> (Tc, E)
+        comm.all_gather_into(B["gath_c"], B["o_c"])
+        B["o_ctx"].view(Tc, P, Eh).copy_(B["gath_c"].permute(1, 0, 2))
         w, b = pm.lin(pre + "context_attn_Wout")
-        _gate_resid(sd3, o_ctx, w, b, c_gate_a, c)
+        _gate_resid(sd3, B["o_ctx"], w, b, c_gate_a, c)
     w, b = pm.lin(pre + "latent_attn_Wout")
-    _gate_resid(sd3, o_rows, w, b, x_gate_a, x_loc)
+    _gate_resid(sd3, B["o_rows"], w, b, x_gate_a, x_loc)
 
-    if dual:
-        qkv2 = torch.empty((1, Tl, 3 * E), device=c.device, dtype=torch.bfloat16)
+    if dual:  # image-only attention of the dual blocks
         w, b = pm.lin(pre + "latent_dual_to_qkv")
         wq, wk = rms("latent_dual")
-        sd3.qkv_project(h_x2, w, b, wq, wk, 1e-6, qkv2, 1, Tl, Tl, 0, E)
-        recv = comm.all_to_all(split_heads_for_send(qkv2[0], P))
-        att_in = recv.reshape(1, P * Tl, 3 * Eh).contiguous()
-        _, o_x = sd3.attention(att_in, 1, P * Tl, NH // P, 0, scale)
-        o_rows = assemble_rows(comm.all_to_all(split_tokens_for_send(o_x[0], P)))
+        sd3.qkv_project_groups(B["h_x2"], w, b, wq, wk, 1e-6, B["send"], E, P)
+        comm.all_to_all_into(B["att2"][0], B["send"])
+        _attention_into(sd3, B["att2"], Tx, NH // P, 0, scale, None, B["o_x"])
+        comm.all_to_all_into(B["recv_o"], B["o_x"])
+        B["o_rows"].view(Tl, P, Eh).copy_(B["recv_o"].permute(1, 0, 2))
         w, b = pm.lin(pre + "latent_dual_attn_Wout")
-        _gate_resid(sd3, o_rows, w, b, ch(xm, 8), x_loc)
+        _gate_resid(sd3, B["o_rows"], w, b, ch(xm, 8), x_loc)
 
-    h_x, _ = _ln_mod(sd3, x_loc, E, 1e-6, x_shift_m, x_scale_m)
+    _ln_mod(sd3, x_loc, E, 1e-6, x_shift_m, x_scale_m, B["h_x"])
     w, b = pm.lin(pre + "latent_mlp.lin1")
-    hid = sd3.linear(h_x, w, b, act=sd3.ACT_GELU_TANH)
+    _linear_into(sd3, B["h_x"], w, b, B["hid_x"], act=sd3.ACT_GELU_TANH)
     w, b = pm.lin(pre + "latent_mlp.lin2")
-    _gate_resid(sd3, hid, w, b, x_gate_m, x_loc)
+    _gate_resid(sd3, B["hid_x"], w, b, x_gate_m, x_loc)
     if not last:
-        h_c, _ = _ln_mod(sd3, c, E, 1e-6, c_shift_m, c_scale_m)
+        _ln_mod(sd3, c, E, 1e-6, c_shift_m, c_scale_m, B["h_c"])
         w, b = pm.lin(pre + "context_mlp.lin1")
-        hid = sd3.linear(h_c, w, b, act=sd3.ACT_GELU_TANH)
+        _linear_into(sd3, B["h_c"], w, b, B["hid_c"], act=sd3.ACT_GELU_TANH)
         w, b = pm.lin(pre + "context_mlp.lin2")
-        _gate_resid(sd3, hid, w, b, c_gate_m, c)
+        _gate_resid(sd3, B["hid_c"], w, b, c_gate_m, c)
 
 
 def dit_forward_sharded(pm, pooled, captions, latent, timesteps, comm):
@@ -210,9 +322,12 @@ def dit_forward_sharded(pm, pooled, captions, latent, timesteps, comm):
         raise sd3.Sd3Error("sequence sharding handles one sample at a time")
     hp, wp = H // p, W // p
     Tx = hp * wp
-    if Tx % P or NH % P:
-        raise sd3.Sd3Error("image tokens (%d) and heads (%d) must divide by the number of ranks (%d)" % (Tx, NH, P))
+    if Tx % P or NH % P or hp % P:
+        raise sd3.Sd3Error("image rows (%d), tokens (%d) and heads (%d) must divide by the number of ranks (%d)"
+                           % (hp, Tx, NH, P))
     Tl = Tx // P
+    Tc = captions.shape[1]
+    bufs = pm.buffers(Tc, Tl, P, True)
     # conditioning vector (replicated)
     emb = sd3.sinusoidal_embedding(timesteps.float().contiguous(), 256)
     w, b = pm.lin("timestep_mlp.0")
@@ -223,26 +338,33 @@ def dit_forward_sharded(pm, pooled, captions, latent, timesteps, comm):
     ph = sd3.skinny_linear(pooled.float().contiguous(), w, b, None, act=1)
     w, b = pm.lin("pooled_mlp.2")
     y = sd3.skinny_linear(ph, w, b, tout, act=1)
-    # context stream (replicated) and the local slice of the image stream
+    # every AdaLN vector of the step from one GEMM with M = 1 over the concatenated matrices
+    if pm.ada_total % 64 == 0 and E % 64 == 0:
+        _linear_into(sd3, sd3.cast(y, torch.bfloat16), pm.ada_w, pm.ada_b, bufs["mod"])
+        mod = bufs["mod"][0]
+    else:
+        mod = sd3.skinny_linear(y, pm.ada_w, pm.ada_b)[0]
+    # context stream (replicated) and the local rows of the image stream: rank r owns the
+    # patch rows [r * hp / P, (r + 1) * hp / P), i.e. a contiguous block of latent rows
     w, b = pm.lin("captions_linear")
     c = sd3.linear(captions[0].to(torch.bfloat16).contiguous(), w, b, out_dtype=torch.float32)
     pos = sd3.pos_embed_table(hp, wp, E, cfg["pos_embed_max_size"], cfg["base_height"] // p)
+    hl = hp // P
+    lat_loc = latent[:, :, rank * hl * p:(rank + 1) * hl * p, :].to(torch.bfloat16).contiguous()
     w, b = pm.lin("to_patch.conv")
-    x_full = sd3.patch_embed(latent.to(torch.bfloat16).contiguous(), w, b, pos, p, E)
-    x_loc = x_full[rank * Tl:(rank + 1) * Tl].contiguous()
-    del x_full
+    x_loc = sd3.patch_embed(lat_loc, w, b, pos[rank * Tl:(rank + 1) * Tl].contiguous(), p, E)
     dual = set(int(l) for l in cfg["dual_attention_layers"])
     L = cfg["num_layers"]
     for l in range(L):
         last = l == L - 1
-        block_forward(pm, l, y, c, x_loc, comm, last, (l in dual) and not last)
+        block_forward(pm, l, mod, c, x_loc, comm, last, (l in dual) and not last)
     # final layer on the local rows, then gather the rows and undo the patching
-    w, b = pm.lin("ada_ln_out.linear")
-    fm = sd3.skinny_linear(y, w, b)[0]
-    h, _ = sd3.layernorm_modulate(x_loc, 1, Tl, E, 1e-5, fm[E:2 * E], fm[0:E], mod_stride=0)
+    off, n = pm.ada_off["ada_ln_out.linear"]
+    fm = mod[off:off + n]
+    _ln_mod(sd3, x_loc, E, 1e-5, fm[E:2 * E], fm[0:E], bufs["h_x"])
     w, b = pm.lin("linear_out")
-    o_loc = sd3.linear(h, w, b, out_dtype=torch.float32)          # (Tl, p*p*C)
-    o = comm.all_gather(o_loc).reshape(Tx, p * p * C)             # rank-major == token order
+    o_loc = sd3.linear(bufs["h_x"], w, b, out_dtype=torch.float32)  # (Tl, p*p*C)
+    o = comm.all_gather(o_loc).reshape(Tx, p * p * C)               # rank-major == token order
     o = o.view(1, hp, wp, p, p, C)
     o = torch.einsum("bhwpqc->bchpwq", o).reshape(1, C, H, W).contiguous()
     return o

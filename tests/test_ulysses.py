@@ -95,3 +95,51 @@ def test_sharded_forward_two_gpus_matches_golden():
         rel = ((ret[r] - g["out"]).norm() / g["out"].norm()).item()
         assert rel < 1e-2, rel
     assert torch.equal(ret[0], ret[1])
+
+
+@pytest.mark.gpu
+def test_sharded_forward_one_rank_matches_golden():
+    """The sharded forward with the one-rank communicator (every exchange is a copy): the
+    whole sequence-parallel code path on a single GPU against the golden toy model."""
+    sd3 = load_binding()
+    U = load_ulysses()
+    g = golden("model_toy.pt")
+    pm = U.PackedModel(sd3, g["params"], g["config"])
+    comm = U.LocalComm()
+    outs = [U.dit_forward_sharded(pm, g["pooled"][b:b + 1].cuda(), g["captions"][b:b + 1].cuda(),
+                                  g["latent"][b:b + 1].cuda(), g["timesteps"][b:b + 1].cuda(), comm)
+            for b in range(g["latent"].shape[0])]
+    torch.cuda.synchronize()
+    assert sd3.device_status() == 0
+    out = torch.cat(outs, 0).cpu()
+    assert ((out - g["out"]).norm() / g["out"].norm()).item() < 1e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,E,K,G", [(300, 256, 256, 2), (512, 512, 256, 4), (77, 192, 1536, 1), (1024, 1536, 1536, 8)])
+def test_qkv_project_head_group_layout(rows, E, K, G):
+    """sd3_qkv_project_groups writes (groups, rows, 3, E/groups): the all-to-all send layout,
+    equal to re-laying the plain (rows, 3E) projection with split_heads_for_send."""
+    sd3 = load_binding()
+    U = load_ulysses()
+    gen = torch.Generator(device="cuda").manual_seed(rows + G)
+    x = torch.randn(rows, K, device="cuda", generator=gen).bfloat16()
+    w = (torch.randn(3 * E, K, device="cuda", generator=gen) * 0.05).bfloat16()
+    b = torch.randn(3 * E, device="cuda", generator=gen) * 0.1
+    wq = 1.0 + 0.2 * torch.randn(64, device="cuda", generator=gen)
+    wk = 1.0 + 0.2 * torch.randn(64, device="cuda", generator=gen)
+    out = torch.empty(G, rows, 3, E // G, device="cuda", dtype=torch.bfloat16)
+    sd3.qkv_project_groups(x, w, b, wq, wk, 1e-6, out, E, G)
+    # reference: fp32 linear + per-head RMSNorm on q and k, then the re-layout
+    y = x.float() @ w.float().t() + b
+    q, k, v = y.split(E, dim=-1)
+
+    def rms(t, wt):
+        t = t.view(rows, E // 64, 64)
+        return (t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + 1e-6) * wt).view(rows, E)
+
+    ref = torch.cat([rms(q, wq), rms(k, wk), v], -1)
+    ref = U.split_heads_for_send(ref.contiguous(), G)
+    torch.cuda.synchronize()
+    assert sd3.device_status() == 0
+    assert ((out.float() - ref).norm() / ref.norm()).item() < 1e-2
