@@ -141,6 +141,21 @@ SD3_API int sd3_attention_generic(const void* q, const void* k, const void* v, l
                           int B, int T, int num_heads, int head_dim, void* out, long ldo,
                           int out_dtype, float scale, void* stream);
 
+/* Attention with separate query and key lengths (fp32 arithmetic, head_dim <= 128):
+ * q (B, Tq, heads*head_dim) with leading dimension ldq, k and v (B, Tk, heads*head_dim)
+ * with leading dimension ldkv; out (B, Tq, heads*head_dim).  `mha` with L != T
+ * (modules.cpp:901-918, module_tests/attention.py:51-83). */
+SD3_API int sd3_cross_attention(const void* q, const void* k, const void* v, long ldq, long ldkv, int in_dtype,
+                                int B, int Tq, int Tk, int num_heads, int head_dim, void* out, long ldo,
+                                int out_dtype, float scale, void* stream);
+
+/* Stand-alone 2-D convolution with square stride and zero padding: x (B,C,H,W) and out
+ * (B,O,Ho,Wo) of io_dtype, weights (O,C,kh,kw) and bias (O) fp32; Ho = (H + 2 padding - kh) /
+ * stride + 1.  Off the denoiser's path (its patch embedding is sd3_patch_embed); replaces
+ * conv2d (modules.cpp:1037-1062) for the general shapes of module_tests/conv2d.py. */
+SD3_API int sd3_conv2d(const void* x, int io_dtype, const float* w_f32, const float* bias, void* out, int B,
+                       int C, int H, int W, int O, int kh, int kw, int stride, int padding, void* stream);
+
 /* out_i = LayerNorm(x; eps, no affine) * (1 + scale_i[b]) + shift_i[b] for one
  * or two modulations (out2/shift2/scale2 NULL for one).  x (B*T, E) f32; the
  * modulation vectors are f32 rows mod_stride floats apart; outputs bf16 or f32.

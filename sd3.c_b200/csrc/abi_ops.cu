@@ -220,6 +220,27 @@ int sd3_attention_generic(const void* q, const void* k, const void* v, long ld, 
                                0, nullptr, out, ldo, out_dtype == SD3_DTYPE_F32, scale, S(stream));
 }
 
+int sd3_cross_attention(const void* q, const void* k, const void* v, long ldq, long ldkv, int in_dtype, int B,
+                        int Tq, int Tk, int num_heads, int head_dim, void* out, long ldo, int out_dtype, float scale,
+                        void* stream) {
+  if (!dtype_ok(in_dtype) || !dtype_ok(out_dtype) || Tk <= 0) {
+    set_last_error("sd3_cross_attention: bad dtype or key count");
+    return SD3_ERR_INVALID_ARG;
+  }
+  return launch_attention_simt(q, k, v, ldq, in_dtype == SD3_DTYPE_F32, B, Tq, num_heads, head_dim, 0, nullptr, out,
+                               ldo, out_dtype == SD3_DTYPE_F32, scale, S(stream), Tk, ldkv);
+}
+
+int sd3_conv2d(const void* x, int io_dtype, const float* w_f32, const float* bias, void* out, int B, int C, int H,
+               int W, int O, int kh, int kw, int stride, int padding, void* stream) {
+  if (!dtype_ok(io_dtype)) {
+    set_last_error("sd3_conv2d: bad io_dtype %d", io_dtype);
+    return SD3_ERR_INVALID_ARG;
+  }
+  return launch_conv2d_direct(x, io_dtype == SD3_DTYPE_F32, w_f32, bias, out, B, C, H, W, O, kh, kw, stride, padding,
+                              S(stream));
+}
+
 int sd3_layernorm_modulate(const float* x, int B, int T, int E, float eps, const float* shift1,
                            const float* scale1, void* out1, const float* shift2,
                            const float* scale2, void* out2, long mod_stride, int out_dtype,

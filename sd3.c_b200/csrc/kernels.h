@@ -110,10 +110,11 @@ int launch_attention_bf16(const bf16* qkv, int B, int T, int NH, int Tc, bf16* o
                           float scale, int* dev_status, cudaStream_t stream, int out_e4m3 = 0);
 
 // Generic SIMT attention (any head_dim <= 128, fp32 or bf16 in, fp32 math).
-// q, k, v: row (b*T + t) at base + row*ld + h*D.  out rows split like above.
+// q: row (b*T + t) at base + row*ld + h*D; k, v: row (b*L + j) at base + row*ldk + h*D
+// (L keys per sample; L <= 0 means L = T, ldk <= 0 means ldk = ld).  out rows split like above.
 int launch_attention_simt(const void* q, const void* k, const void* v, long ld, int in_f32, int B,
                           int T, int NH, int D, int Tc, void* out_c, void* out_x, long ldo,
-                          int out_f32, float scale, cudaStream_t stream);
+                          int out_f32, float scale, cudaStream_t stream, int L = 0, long ldk = 0);
 
 // ----------------------------------------------------------------------------
 // Memory-bound kernels
@@ -142,6 +143,10 @@ int launch_pos_table(float* table, int h, int w, int E, int pmax, int base_size,
 // latent (B, C, H, W) fp32/bf16 -> patches (B*h*w, C*p*p) bf16 or fp32, k = c*p*p + ph*p + pw
 int launch_patchify(const void* latent, int in_f32, void* out, int out_f32, int B, int C, int H,
                     int W, int p, cudaStream_t stream);
+
+// generic conv2d (square stride, zero padding), in/out (B,C,H,W) fp32 or bf16, weights/bias fp32
+int launch_conv2d_direct(const void* in, int io_f32, const float* w, const float* bias, void* out, int B, int C,
+                         int H, int W, int O, int kh, int kw, int stride, int pad, cudaStream_t stream);
 
 // element-wise casts / transposes used by weight packing and the per-op API
 int launch_cast_f32_to_bf16(const float* in, bf16* out, long n, cudaStream_t stream);

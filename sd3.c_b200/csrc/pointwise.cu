@@ -625,4 +625,69 @@ int launch_rmsnorm_heads(void* x, int x_f32, long ld, long rows, int col0, int n
   return after_launch("rmsnorm_heads_kernel");
 }
 
+
+// ----------------------------------------------------------------------------
+// Generic 2-D convolution (any square stride and zero padding), one thread per
+// output element, fp32 accumulation.  Off the denoiser's path (its patch
+// embedding is kernel == stride and runs as a gather + tensor-core GEMM); this
+// is the stand-alone `conv2d` operator of the reference (conv2d,
+// modules.cpp:1037-1062) for the shapes its own script uses.
+// ----------------------------------------------------------------------------
+namespace {
+template <typename T>
+__global__ void conv2d_direct_kernel(const T* __restrict__ in, const float* __restrict__ w,
+                                     const float* __restrict__ bias, T* __restrict__ out, int B, int C, int H,
+                                     int W, int O, int kh, int kw, int stride, int pad, int Ho, int Wo) {
+  const long total = static_cast<long>(B) * O * Ho * Wo;
+  for (long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long>(gridDim.x) * blockDim.x) {
+    const int xo = static_cast<int>(idx % Wo);
+    const int yo = static_cast<int>((idx / Wo) % Ho);
+    const int o = static_cast<int>((idx / (static_cast<long>(Wo) * Ho)) % O);
+    const int b = static_cast<int>(idx / (static_cast<long>(Wo) * Ho * O));
+    float acc = bias ? bias[o] : 0.f;
+    for (int c = 0; c < C; ++c) {
+      const T* ip = in + (static_cast<long>(b) * C + c) * H * W;
+      const float* wp = w + (static_cast<long>(o) * C + c) * kh * kw;
+      for (int ky = 0; ky < kh; ++ky) {
+        const int y = yo * stride - pad + ky;
+        if (y < 0 || y >= H) continue;
+        for (int kx = 0; kx < kw; ++kx) {
+          const int x = xo * stride - pad + kx;
+          if (x < 0 || x >= W) continue;
+          float v;
+          if constexpr (sizeof(T) == 4) v = ip[static_cast<long>(y) * W + x];
+          else v = __bfloat162float(ip[static_cast<long>(y) * W + x]);
+          acc = fmaf(v, wp[ky * kw + kx], acc);
+        }
+      }
+    }
+    if constexpr (sizeof(T) == 4) out[idx] = acc;
+    else out[idx] = __float2bfloat16(acc);
+  }
+}
+}  // namespace
+
+int launch_conv2d_direct(const void* in, int io_f32, const float* w, const float* bias, void* out, int B, int C,
+                         int H, int W, int O, int kh, int kw, int stride, int pad, cudaStream_t stream) {
+  if (!in || !w || !out || B <= 0 || C <= 0 || H <= 0 || W <= 0 || O <= 0 || kh <= 0 || kw <= 0 || stride <= 0 ||
+      pad < 0 || H + 2 * pad < kh || W + 2 * pad < kw) {
+    set_last_error("conv2d: invalid argument");
+    return ST_INVALID_ARG;
+  }
+  const int Ho = (H + 2 * pad - kh) / stride + 1, Wo = (W + 2 * pad - kw) / stride + 1;
+  const long total = static_cast<long>(B) * O * Ho * Wo;
+  const long blocks = (total + 255) / 256;
+  const unsigned grid = static_cast<unsigned>(blocks < device_sm_count() * 16L ? blocks : device_sm_count() * 16L);
+  if (io_f32)
+    conv2d_direct_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(in), w, bias,
+                                                          static_cast<float*>(out), B, C, H, W, O, kh, kw, stride,
+                                                          pad, Ho, Wo);
+  else
+    conv2d_direct_kernel<bf16><<<grid, 256, 0, stream>>>(static_cast<const bf16*>(in), w, bias,
+                                                         static_cast<bf16*>(out), B, C, H, W, O, kh, kw, stride, pad,
+                                                         Ho, Wo);
+  return after_launch("conv2d_direct_kernel");
+}
+
 }  // namespace sd3

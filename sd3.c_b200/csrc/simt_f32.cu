@@ -126,7 +126,7 @@ template <> __device__ __forceinline__ float ld_as_float<bf16>(const bf16* p) { 
 template <typename IT, typename OT, int DV>  // DV = ceil(D / 32) values of q per lane
 __global__ void __launch_bounds__(128)
 attention_simt_kernel(const IT* __restrict__ q, const IT* __restrict__ k, const IT* __restrict__ v,
-                      long ld, int B, int T, int NH, int D, int Tc, OT* __restrict__ out_c,
+                      long ld, long ldk, int B, int T, int L, int NH, int D, int Tc, OT* __restrict__ out_c,
                       OT* __restrict__ out_x, long ldo, float scale) {
   extern __shared__ float sq[];  // per warp: D floats of the scaled query
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -145,9 +145,9 @@ attention_simt_kernel(const IT* __restrict__ q, const IT* __restrict__ k, const 
   float o[DV * 32];
 #pragma unroll
   for (int i = 0; i < DV * 32; ++i) o[i] = 0.f;
-  for (int j = lane; j < T; j += 32) {
-    const IT* kp = k + (static_cast<long>(b) * T + j) * ld + h * D;
-    const IT* vp = v + (static_cast<long>(b) * T + j) * ld + h * D;
+  for (int j = lane; j < L; j += 32) {  // L keys per sample (== T for self-attention)
+    const IT* kp = k + (static_cast<long>(b) * L + j) * ldk + h * D;
+    const IT* vp = v + (static_cast<long>(b) * L + j) * ldk + h * D;
     float s = 0.f;
     for (int i = 0; i < D; ++i) s = fmaf(myq[i], ld_as_float(kp + i), s);
     const float m_new = fmaxf(m, s);
@@ -185,7 +185,7 @@ attention_simt_kernel(const IT* __restrict__ q, const IT* __restrict__ k, const 
 }
 
 template <typename IT, typename OT>
-int launch_attn_inst(const void* q, const void* k, const void* v, long ld, int B, int T, int NH,
+int launch_attn_inst(const void* q, const void* k, const void* v, long ld, long ldk, int B, int T, int L, int NH,
                      int D, int Tc, void* out_c, void* out_x, long ldo, float scale,
                      cudaStream_t stream) {
   const long total = static_cast<long>(B) * NH * T;
@@ -194,13 +194,13 @@ int launch_attn_inst(const void* q, const void* k, const void* v, long ld, int B
   const size_t smem = static_cast<size_t>(wpb) * D * sizeof(float);
   if (D <= 32)
     attention_simt_kernel<IT, OT, 1><<<grid, wpb * 32, smem, stream>>>(
-        (const IT*)q, (const IT*)k, (const IT*)v, ld, B, T, NH, D, Tc, (OT*)out_c, (OT*)out_x, ldo, scale);
+        (const IT*)q, (const IT*)k, (const IT*)v, ld, ldk, B, T, L, NH, D, Tc, (OT*)out_c, (OT*)out_x, ldo, scale);
   else if (D <= 64)
     attention_simt_kernel<IT, OT, 2><<<grid, wpb * 32, smem, stream>>>(
-        (const IT*)q, (const IT*)k, (const IT*)v, ld, B, T, NH, D, Tc, (OT*)out_c, (OT*)out_x, ldo, scale);
+        (const IT*)q, (const IT*)k, (const IT*)v, ld, ldk, B, T, L, NH, D, Tc, (OT*)out_c, (OT*)out_x, ldo, scale);
   else
     attention_simt_kernel<IT, OT, 4><<<grid, wpb * 32, smem, stream>>>(
-        (const IT*)q, (const IT*)k, (const IT*)v, ld, B, T, NH, D, Tc, (OT*)out_c, (OT*)out_x, ldo, scale);
+        (const IT*)q, (const IT*)k, (const IT*)v, ld, ldk, B, T, L, NH, D, Tc, (OT*)out_c, (OT*)out_x, ldo, scale);
   return after_launch("attention_simt_kernel");
 }
 
@@ -226,19 +226,21 @@ int launch_gemm_f32(const float* A, long lda, const float* W, long ldw, int M, i
 
 int launch_attention_simt(const void* q, const void* k, const void* v, long ld, int in_f32, int B,
                           int T, int NH, int D, int Tc, void* out_c, void* out_x, long ldo,
-                          int out_f32, float scale, cudaStream_t stream) {
+                          int out_f32, float scale, cudaStream_t stream, int L, long ldk) {
+  if (L <= 0) L = T;
+  if (ldk <= 0) ldk = ld;
   if (!q || !k || !v || !out_x || B <= 0 || T <= 0 || NH <= 0 || D <= 0 || D > 128 || Tc < 0 ||
       Tc > T) {
     set_last_error("attention_generic: invalid argument (head_dim %d must be <= 128)", D);
     return ST_INVALID_ARG;
   }
   if (in_f32 && out_f32)
-    return launch_attn_inst<float, float>(q, k, v, ld, B, T, NH, D, Tc, out_c, out_x, ldo, scale, stream);
+    return launch_attn_inst<float, float>(q, k, v, ld, ldk, B, T, L, NH, D, Tc, out_c, out_x, ldo, scale, stream);
   if (in_f32)
-    return launch_attn_inst<float, bf16>(q, k, v, ld, B, T, NH, D, Tc, out_c, out_x, ldo, scale, stream);
+    return launch_attn_inst<float, bf16>(q, k, v, ld, ldk, B, T, L, NH, D, Tc, out_c, out_x, ldo, scale, stream);
   if (out_f32)
-    return launch_attn_inst<bf16, float>(q, k, v, ld, B, T, NH, D, Tc, out_c, out_x, ldo, scale, stream);
-  return launch_attn_inst<bf16, bf16>(q, k, v, ld, B, T, NH, D, Tc, out_c, out_x, ldo, scale, stream);
+    return launch_attn_inst<bf16, float>(q, k, v, ld, ldk, B, T, L, NH, D, Tc, out_c, out_x, ldo, scale, stream);
+  return launch_attn_inst<bf16, bf16>(q, k, v, ld, ldk, B, T, L, NH, D, Tc, out_c, out_x, ldo, scale, stream);
 }
 
 }  // namespace sd3

@@ -61,6 +61,11 @@ struct ModelHolder {
 struct CacheEntry {
   std::string key;
   std::shared_ptr<ModelHolder> model;
+  // The parameter tensors the model was packed from.  The key identifies them by storage
+  // address and version counter; holding them keeps those storages alive, so an address in a
+  // key can never be that of a newer tensor that reused freed memory (in-place writes bump the
+  // version counter and miss the cache as they should).
+  std::vector<Tensor> keep;
 };
 
 std::mutex g_mu;
@@ -111,7 +116,10 @@ std::shared_ptr<ModelHolder> get_model(const sd3_config& cfg, const ParamDict& p
   int missing = 0;
   ok(sd3_model_finalize(holder->m, &missing), "sd3_model_finalize");
   if (g_cache.size() >= 4) g_cache.erase(g_cache.begin());
-  g_cache.push_back({key, holder});
+  std::vector<Tensor> keep;
+  keep.reserve(params.size());
+  for (const auto& kv : params) keep.push_back(kv.second);
+  g_cache.push_back({key, holder, std::move(keep)});
   return holder;
 }
 
@@ -281,17 +289,32 @@ std::vector<Tensor> RMSNorm_forward(Tensor& x_in, Tensor& w, float eps, bool sav
   return {x};
 }
 
-// conv2d in its patch-embedding form: kernel == stride, no padding
+// conv2d(x (B,C,H,W), kernel (O,I,kh,kw), bias, stride, padding): the patch-embedding form
+// (kernel == stride, padding 0) runs as gather + tensor-core GEMM, every other shape through the
+// stand-alone convolution kernel
 Tensor conv2d_forward(Tensor& x_in, Tensor& kernel, Tensor& bias, int stride, int padding) {
   Tensor x = dev(x_in, "x");
   c10::cuda::CUDAGuard guard(x.device());
   Tensor k = dev(kernel, "kernel");
   TORCH_CHECK(x.dim() == 4 && k.dim() == 4, "conv2d: (B,C,H,W) input and (O,I,kh,kw) kernel expected");
-  TORCH_CHECK(padding == 0 && k.size(2) == stride && k.size(3) == stride,
-              "conv2d: only the patch-embedding form (kernel == stride, padding 0) is provided");
+  TORCH_CHECK(k.size(1) == x.size(1), "conv2d: kernel and input channel counts differ");
+  TORCH_CHECK(stride > 0 && padding >= 0, "conv2d: stride must be positive and padding non-negative");
   const int B = x.size(0), C = x.size(1), H = x.size(2), W = x.size(3), O = k.size(0), p = stride;
-  const int hp = H / p, wp = W / p, Kp = C * p * p;
   Tensor bf = bias_f32(bias, O);
+  const bool patch_form = padding == 0 && k.size(2) == stride && k.size(3) == stride && H % p == 0 && W % p == 0 &&
+                          (C * p * p) % 8 == 0 && O % 8 == 0;
+  if (!patch_form) {
+    const int kh = k.size(2), kw = k.size(3);
+    TORCH_CHECK(H + 2 * padding >= kh && W + 2 * padding >= kw, "conv2d: kernel larger than the padded input");
+    const int Ho = (H + 2 * padding - kh) / stride + 1, Wo = (W + 2 * padding - kw) / stride + 1;
+    Tensor wf = k.to(torch::kFloat32).contiguous();
+    Tensor out = torch::empty({B, O, Ho, Wo}, x.options());
+    ok(sd3_conv2d(x.data_ptr(), tag(x), wf.data_ptr<float>(), bf.data_ptr<float>(), out.data_ptr(), B, C, H, W, O,
+                  kh, kw, stride, padding, stream()),
+       "sd3_conv2d");
+    return out;
+  }
+  const int hp = H / p, wp = W / p, Kp = C * p * p;
   Tensor zero_table = torch::zeros({(int64_t)hp * wp, O}, x.options().dtype(torch::kFloat32));
   Tensor tokens = torch::empty({(int64_t)B * hp * wp, O}, x.options().dtype(torch::kFloat32));
   Tensor w16 = k.reshape({O, Kp}).to(torch::kBFloat16).contiguous();
@@ -323,16 +346,24 @@ Tensor positional_embedding2D_forward(int emb_dim, int height, int width, int ba
   return out;
 }
 
-// mha(Q (B,T,C), K (B,L,C), V (B,L,C), num_heads) -> (B,T,C); self-attention shapes (L == T)
+// mha(Q (B,T,C), K (B,L,C), V (B,L,C), num_heads) -> (B,T,C); L may differ from T
 Tensor mha(Tensor& Q, Tensor& K, Tensor& V, int num_heads) {
   Tensor q = dev(Q, "Q"), k = dev(K, "K"), v = dev(V, "V");
   c10::cuda::CUDAGuard guard(q.device());
-  TORCH_CHECK(q.dim() == 3 && k.sizes() == q.sizes() && v.sizes() == q.sizes(),
-              "mha: Q, K, V of identical shape (B,T,C) expected");
-  const int B = q.size(0), T = q.size(1), C = q.size(2);
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.sizes() == k.sizes() && k.size(0) == q.size(0) &&
+                  k.size(2) == q.size(2) && k.scalar_type() == q.scalar_type() && v.scalar_type() == q.scalar_type(),
+              "mha: Q (B,T,C) and K, V (B,L,C) of one dtype expected");
+  const int B = q.size(0), T = q.size(1), C = q.size(2), L = k.size(1);
   TORCH_CHECK(C % num_heads == 0, "mha: C must be divisible by num_heads");
   const int D = C / num_heads;
+  TORCH_CHECK(D <= 128, "mha: head_dim above 128 is not provided");
   Tensor out = torch::empty_like(q);
+  if (L != T) {
+    ok(sd3_cross_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(), C, C, tag(q), B, T, L, num_heads, D,
+                           out.data_ptr(), C, tag(out), 1.0f / std::sqrt((float)D), stream()),
+       "sd3_cross_attention");
+    return out;
+  }
   if (q.scalar_type() == torch::kBFloat16 && D == 64) {
     Tensor qkv = torch::cat({q, k, v}, 2).contiguous();
     ok(sd3_attention(qkv.data_ptr(), B, T, num_heads, 0, nullptr, out.data_ptr(),

@@ -65,6 +65,8 @@ PROTOTYPES = {
     "sd3_qkv_project_groups": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "sd3_attention": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p]),
     "sd3_attention_generic": (c_int, [c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_long, c_int, c_float, c_void_p]),
+    "sd3_cross_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_long, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_long, c_int, c_float, c_void_p]),
+    "sd3_conv2d": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "sd3_layernorm_modulate": (c_int, [c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p]),
     "sd3_skinny_linear": (c_int, [c_void_p, c_long, c_void_p, c_int, c_void_p, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int, c_void_p]),
     "sd3_sinusoidal_embedding": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),

@@ -105,13 +105,29 @@ def test_per_op_entry_points(F):
     k = (torch.randn(64, 16, 2, 2, device="cuda") * 0.1).bfloat16().float()
     cb = torch.randn(64, device="cuda")
     assert (F.conv2d(lat, k, cb, 2, 0) - torch.nn.functional.conv2d(lat, k, cb, stride=2)).abs().max().item() < 1e-4
-    with pytest.raises(RuntimeError):
-        F.conv2d(lat, k, cb, 1, 1)
+    # conv2d with other strides / padding (module_tests/conv2d.py), fp32 and bf16
+    xin = torch.randn(2, 3, 17, 19, device="cuda")
+    k3 = torch.randn(5, 3, 3, 3, device="cuda") * 0.2
+    b3 = torch.randn(5, device="cuda")
+    for stride, pad in ((1, 1), (2, 1), (1, 0), (3, 2)):
+        ref = torch.nn.functional.conv2d(xin, k3, b3, stride=stride, padding=pad)
+        got = F.conv2d(xin, k3, b3, stride, pad)
+        assert got.shape == ref.shape and (got - ref).abs().max().item() < 1e-4
+    got = F.conv2d(xin.bfloat16(), k3.bfloat16(), b3, 2, 1)
+    ref = torch.nn.functional.conv2d(xin.bfloat16().float(), k3.bfloat16().float(), b3, stride=2, padding=1)
+    assert got.dtype == torch.bfloat16 and rel_l2(got, ref) < 1e-2
     # mha (module_tests/attention.py shapes: B2 T128 C512 H8 -> head_dim 64)
     q, kk, v = [torch.randn(2, 128, 512, device="cuda") for _ in range(3)]
     ref = O.attention(q.view(2, 128, 8, 64), kk.view(2, 128, 8, 64), v.view(2, 128, 8, 64))
     assert (F.mha(q, kk, v, 8) - ref).abs().max().item() < 1e-4
     assert rel_l2(F.mha(q.bfloat16(), kk.bfloat16(), v.bfloat16(), 8), ref) < 1e-2
+    # mha with a key length other than the query length (module_tests/attention.py: T 128, L 96)
+    k96, v96 = torch.randn(2, 96, 512, device="cuda"), torch.randn(2, 96, 512, device="cuda")
+    ref = torch.nn.functional.scaled_dot_product_attention(
+        q.view(2, 128, 8, 64).transpose(1, 2), k96.view(2, 96, 8, 64).transpose(1, 2),
+        v96.view(2, 96, 8, 64).transpose(1, 2)).transpose(1, 2).reshape(2, 128, 512)
+    assert (F.mha(q, k96, v96, 8) - ref).abs().max().item() < 1e-4
+    assert rel_l2(F.mha(q.bfloat16(), k96.bfloat16(), v96.bfloat16(), 8), ref) < 1e-2
     # mlp with GELU-tanh (the block's MLP)
     x = torch.randn(6, 64, device="cuda")
     W1, b1 = torch.randn(64, 256, device="cuda") * 0.1, torch.randn(256, device="cuda")
