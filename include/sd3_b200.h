@@ -133,6 +133,17 @@ SD3_API int sd3_qkv_project_groups(const void* x_bf16, const void* w_nk_bf16, co
 SD3_API int sd3_attention(const void* qkv_bf16, int B, int T, int num_heads, int Tc, void* out_c_bf16,
                   void* out_x_bf16, float scale, void* stream);
 
+/* sd3_attention with a scratch buffer.  Launches with too few (sample, head, query tile)
+ * units to fill the GPU -- one long sequence with few heads, as on a rank of a
+ * sequence-parallel run -- split the keys of every query tile over several CTAs and merge the
+ * partial results; that needs sd3_attention_scratch_bytes(B, T, num_heads) bytes of scratch
+ * (16-byte aligned; 0 for shapes that fill the GPU anyway, and then scratch may be null).
+ * Same result as sd3_attention up to the rounding of the merge (fp32).  Replaces the same
+ * reference code as sd3_attention. */
+SD3_API long sd3_attention_scratch_bytes(int B, int T, int num_heads);
+SD3_API int sd3_attention_ws(const void* qkv_bf16, int B, int T, int num_heads, int Tc, void* out_c_bf16,
+                             void* out_x_bf16, float scale, void* scratch, long scratch_bytes, void* stream);
+
 /* Generic attention in fp32 arithmetic for any head_dim <= 128: q, k, v are
  * (B, Tq|Tk, num_heads*head_dim) row-major with leading dimension ld elements,
  * dtype in_dtype; out (B, Tq, num_heads*head_dim) of out_dtype.  Stand-in for

@@ -51,6 +51,7 @@
 
 namespace sd3 {
 
+int device_sm_count();
 int encode_tmap_3d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t d0, uint64_t d1,
                    uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0,
                    uint32_t box1, uint32_t box2);
@@ -77,6 +78,13 @@ struct AttnArgs {
   float scale_log2e;
   int out_e4m3;  // outputs are e4m3 bytes (operand of an FP8 out-projection) instead of bf16
   int* status;
+  // Key split (launches with too few CTAs to fill the machine): kv_split CTAs share a query
+  // tile, each takes a contiguous range of the key tiles and leaves its unnormalised output
+  // row (64 fp32), its running maximum and its row sum in part_o / part_ml; a merge kernel
+  // combines them.  kv_split == 1: the CTA normalises and writes the output itself.
+  int kv_split;
+  float* part_o;   // (B, NH, kv_split, T, 64)
+  float* part_ml;  // (B, NH, kv_split, T, 2): maximum (raw score units), row sum
 };
 
 // O *= alpha for this thread's query row (64 fp32 columns in TMEM).  Rare (the
@@ -206,11 +214,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
   int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q0 = blockIdx.x * AT_BM;
+  const int split = blockIdx.x % a.kv_split;  // which share of the keys
+  const int q0 = (blockIdx.x / a.kv_split) * AT_BM;
   const int h = blockIdx.y;
   const int b = blockIdx.z;
   const int T = a.T;
-  const int nkv = (T + AT_BN - 1) / AT_BN;
+  const int nkv_all = (T + AT_BN - 1) / AT_BN;
+  const int jt0 = static_cast<int>(static_cast<long>(nkv_all) * split / a.kv_split);  // first key tile of this CTA
+  const int nkv = static_cast<int>(static_cast<long>(nkv_all) * (split + 1) / a.kv_split) - jt0;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -247,11 +258,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
         // K of tile j - STAGES is free once its scores are complete
         if (j >= AT_STAGES && !mbar_wait(&s_full[st], prev, wc, DEV_TIMEOUT_ATTN_KV)) break;
         mbar_expect_tx(&k_full[st], AT_TILE_BYTES);
-        tma_load_3d(k_smem + st * AT_TILE_BYTES, &tmQKV, &k_full[st], a.E + h * AT_D, j * AT_BN, b);
+        tma_load_3d(k_smem + st * AT_TILE_BYTES, &tmQKV, &k_full[st], a.E + h * AT_D, (jt0 + j) * AT_BN, b);
         // V of tile j - STAGES is free once its products are complete
         if (j >= AT_STAGES && !mbar_wait(&pv_done[st], prev, wc, DEV_TIMEOUT_ATTN_KV)) break;
         mbar_expect_tx(&v_full[st], AT_TILE_BYTES);
-        tma_load_3d(v_smem + st * AT_TILE_BYTES, &tmQKV, &v_full[st], 2 * a.E + h * AT_D, j * AT_BN, b);
+        tma_load_3d(v_smem + st * AT_TILE_BYTES, &tmQKV, &v_full[st], 2 * a.E + h * AT_D, (jt0 + j) * AT_BN, b);
       }
     }
   } else if (warp == 1) {
@@ -308,7 +319,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
     uint32_t ra[32], rb[32], rc[32], rd[32];  // scores of keys 0..31, 32..63, 64..95, 96..127, then packed P
     for (int j = 0; j < nkv; ++j) {
       const int st = j % AT_STAGES;
-      const int kv0 = j * AT_BN;
+      const int kv0 = (jt0 + j) * AT_BN;
       const bool ragged = kv0 + AT_BN > T;
       const int stp = (j + AT_STAGES - 1) % AT_STAGES;               // stage and parity of the
       const uint32_t parp = j >= 1 ? ((j - 1) / AT_STAGES) & 1 : 0;  // previous tile's products
@@ -378,7 +389,19 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
       tmem_ld_32x32b_x32(o_tmem + 32, o1);
       tmem_wait_ld();
       const int t = q0 + row;
-      if (t < T) {
+      if (t < T && a.kv_split > 1) {
+        // partial result of this share of the keys; the merge kernel finishes the row
+        const long prow = ((static_cast<long>(b) * a.NH + h) * a.kv_split + split) * T + t;
+        float4* po = reinterpret_cast<float4*>(a.part_o + prow * AT_D);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          po[i] = make_float4(__uint_as_float(o0[4 * i]), __uint_as_float(o0[4 * i + 1]),
+                              __uint_as_float(o0[4 * i + 2]), __uint_as_float(o0[4 * i + 3]));
+          po[8 + i] = make_float4(__uint_as_float(o1[4 * i]), __uint_as_float(o1[4 * i + 1]),
+                                  __uint_as_float(o1[4 * i + 2]), __uint_as_float(o1[4 * i + 3]));
+        }
+        *reinterpret_cast<float2*>(a.part_ml + prow * 2) = make_float2(m_used, l);
+      } else if (t < T) {
         const float inv = 1.0f / l;
         bf16* dst = nullptr;
         long off = -1;  // element offset of this row's 64 values in out_c / out_x
@@ -449,10 +472,81 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
   }
 }
 
+
+// Combines the kv_split partial results of every query row: with m = max_s m_s and
+// w_s = 2^((m_s - m) c), out = sum_s w_s O_s / sum_s w_s l_s.  One warp per (sample, head,
+// token) row, two output columns per lane; rows go to the context / image outputs like in
+// the attention kernel's own epilogue.
+__global__ void __launch_bounds__(256) attention_merge_kernel(const AttnArgs a) {
+  const long row = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long rows = static_cast<long>(a.B) * a.NH * a.T;
+  if (row >= rows) return;
+  const int t = static_cast<int>(row % a.T);
+  const int h = static_cast<int>((row / a.T) % a.NH);
+  const int b = static_cast<int>(row / (static_cast<long>(a.T) * a.NH));
+  const long p0 = (static_cast<long>(b) * a.NH + h) * a.kv_split * a.T + t;  // split 0; splits are T rows apart
+  float m = -INFINITY;
+  for (int s = 0; s < a.kv_split; ++s) m = fmaxf(m, a.part_ml[(p0 + static_cast<long>(s) * a.T) * 2]);
+  float2 acc = make_float2(0.f, 0.f);
+  float l = 0.f;
+  for (int s = 0; s < a.kv_split; ++s) {
+    const long pr = p0 + static_cast<long>(s) * a.T;
+    const float2 ml = *reinterpret_cast<const float2*>(a.part_ml + pr * 2);
+    const float w = ex2_approx((ml.x - m) * a.scale_log2e);
+    const float2 o = *reinterpret_cast<const float2*>(a.part_o + pr * AT_D + 2 * lane);
+    acc.x = fmaf(w, o.x, acc.x);
+    acc.y = fmaf(w, o.y, acc.y);
+    l = fmaf(w, ml.y, l);
+  }
+  const float inv = 1.0f / l;
+  long off = -1;
+  if (t < a.Tc) {
+    if (a.out_c) off = (static_cast<long>(b) * a.Tc + t) * a.E + h * AT_D;
+  } else {
+    off = (static_cast<long>(b) * (a.T - a.Tc) + (t - a.Tc)) * a.E + h * AT_D;
+  }
+  if (off < 0) return;
+  void* base = t < a.Tc ? static_cast<void*>(a.out_c) : static_cast<void*>(a.out_x);
+  if (a.out_e4m3)
+    reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(base) + off)[lane] = pack_e4m3x2(acc.x * inv, acc.y * inv);
+  else
+    reinterpret_cast<uint32_t*>(static_cast<bf16*>(base) + off)[lane] = pack_bf16x2(acc.x * inv, acc.y * inv);
+}
+
+// Key split for a launch of `ctas` CTAs: the factor (1..4) that fills the last wave best,
+// the split's merge pass discounted by 4 %, each share at least eight key tiles long.
+// Only launches of less than 1.4 waves are split: measured at T = 16717, a launch of 1.33
+// waves (3 heads) gains 9 % from a split, one of 2.66 waves (6 heads) loses 1 % and one of
+// 5.3 waves loses 10 % -- the CTAs of a part-filled last wave have their SM to themselves and
+// run faster, so wave arithmetic overstates what a split can recover.
+int choose_kv_split(long ctas, int nkv) {
+  const long slots = 2L * device_sm_count();
+  if (ctas * 10 >= slots * 14) return 1;
+  auto fill = [&](long n) { return static_cast<double>(n) / static_cast<double>(((n + slots - 1) / slots) * slots); };
+  int best = 1;
+  double best_fill = fill(ctas);
+  for (int sp = 2; sp <= 4; ++sp) {
+    if (nkv / sp < 8) break;
+    const double f = 0.96 * fill(ctas * sp);
+    if (f > best_fill + 0.02) { best = sp; best_fill = f; }
+  }
+  return best;
+}
+
 }  // namespace
 
+size_t attention_scratch_bytes(int B, int T, int NH) {
+  // what the key split chosen for this shape needs: partial outputs and (maximum, row sum) pairs
+  if (B <= 0 || T <= 0 || NH <= 0) return 0;
+  const int qtiles = (T + AT_BM - 1) / AT_BM, nkv = (T + AT_BN - 1) / AT_BN;
+  const int sp = choose_kv_split(static_cast<long>(qtiles) * NH * B, nkv);
+  return sp > 1 ? static_cast<size_t>(B) * NH * sp * T * (AT_D + 2) * sizeof(float) : 0;
+}
+
 int launch_attention_bf16(const bf16* qkv, int B, int T, int NH, int Tc, bf16* out_c, bf16* out_x,
-                          float scale, int* dev_status, cudaStream_t stream, int out_e4m3) {
+                          float scale, int* dev_status, cudaStream_t stream, int out_e4m3, void* scratch,
+                          size_t scratch_bytes) {
   if (!qkv || !out_x || B <= 0 || T <= 0 || NH <= 0 || Tc < 0 || Tc > T ||
       (reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(out_x) & 15) ||
       (reinterpret_cast<uintptr_t>(out_c) & 15)) {
@@ -487,9 +581,26 @@ int launch_attention_bf16(const bf16* qkv, int B, int T, int NH, int Tc, bf16* o
   a.scale_log2e = scale * 1.4426950408889634f;
   a.out_e4m3 = out_e4m3;
   a.status = dev_status;
-  const dim3 grid((T + AT_BM - 1) / AT_BM, NH, B);
+  const int qtiles = (T + AT_BM - 1) / AT_BM, nkv = (T + AT_BN - 1) / AT_BN;
+  a.kv_split = 1;
+  a.part_o = nullptr;
+  a.part_ml = nullptr;
+  if (scratch && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0) {
+    const int sp = choose_kv_split(static_cast<long>(qtiles) * NH * B, nkv);
+    const size_t rows = static_cast<size_t>(B) * NH * sp * T;
+    if (sp > 1 && rows * (AT_D + 2) * sizeof(float) <= scratch_bytes && static_cast<long>(qtiles) * sp <= 0x7fffffffL) {
+      a.kv_split = sp;
+      a.part_o = static_cast<float*>(scratch);
+      a.part_ml = a.part_o + rows * AT_D;
+    }
+  }
+  const dim3 grid(qtiles * a.kv_split, NH, B);
   attention_tcgen05_kernel<<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(tm, a);
-  return after_launch("attention_tcgen05_kernel");
+  int lrc = after_launch("attention_tcgen05_kernel");
+  if (lrc || a.kv_split == 1) return lrc;
+  const long warps = static_cast<long>(B) * NH * T;
+  attention_merge_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, stream>>>(a);
+  return after_launch("attention_merge_kernel");
 }
 
 }  // namespace sd3

@@ -63,6 +63,8 @@ struct Workspace {
   void *cap_in, *patches, *h_c, *h_x, *h_x2, *qkv, *qkv2, *o_c, *o_x, *o_x2, *hid_x, *hid_c;
   bf16* y_bf = nullptr;  // conditioning vector as a GEMM operand
   void* a8 = nullptr;    // FP8 mode: e4m3 copy of the current GEMM's left operand
+  void* attn_scratch = nullptr;  // partial results of key-split attention launches (small batches, long sequences)
+  size_t attn_scratch_bytes = 0;
   // position table cache
   float* pos = nullptr;
   int pos_h = 0, pos_w = 0;
@@ -255,7 +257,16 @@ int reserve_ws(sd3_model* m, int B, int Tc, int Tx) {
       {&w.o_c, nTc * E * ab}, {&w.o_x, nTx * E * ab}, {&w.o_x2, nTx * E * ab},
       {&w.hid_x, nTx * F * ab}, {&w.hid_c, nTc * F * ab},
       {&w.a8, m->fp8 ? (nTx > nTc ? nTx : nTc) * F : 16},
+      {&w.attn_scratch, 16},
   };
+  // key-split attention (head_dim 64 tensor-core path): the larger need of the joint and the image-only call
+  w.attn_scratch_bytes = 0;
+  if (!m->f32 && m->D == 64) {
+    const size_t a = attention_scratch_bytes(B, static_cast<int>(T), m->NH);
+    const size_t b2 = attention_scratch_bytes(B, Tx, m->NH);
+    w.attn_scratch_bytes = a > b2 ? a : b2;
+    if (w.attn_scratch_bytes > 0) items.back().bytes = w.attn_scratch_bytes;
+  }
   size_t total = 0;
   for (auto& it : items) total += align_up(it.bytes, 256);
   void* base = nullptr;
@@ -364,7 +375,8 @@ int run_attention(sd3_model* m, const void* qkv, int B, int T, int Tc, void* o_c
   if (!m->f32 && m->D == 64)
     return launch_attention_bf16(static_cast<const bf16*>(qkv), B, T, m->NH, Tc,
                                  static_cast<bf16*>(o_c), static_cast<bf16*>(o_x), scale, m->status,
-                                 st, out_e4m3 ? 1 : 0);
+                                 st, out_e4m3 ? 1 : 0, m->ws.attn_scratch_bytes ? m->ws.attn_scratch : nullptr,
+                                 m->ws.attn_scratch_bytes);
   if (out_e4m3) {
     set_last_error("e4m3 attention output needs head_dim 64");
     return ST_UNSUPPORTED;

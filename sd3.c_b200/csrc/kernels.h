@@ -106,8 +106,13 @@ int launch_gemm_grouped(const GemmProblem& a, const GemmProblem& b, int operand_
 // to out_x[(b*(T-Tc) + t - Tc), :]; out_c may be null (context rows dropped).
 // ----------------------------------------------------------------------------
 // out_e4m3: out_c / out_x receive one e4m3 byte per element (rows E bytes apart) instead of bf16.
+// scratch (optional, 16-byte aligned, attention_scratch_bytes(B, T, NH) bytes, which is 0 for
+// shapes that fill the machine anyway): lets launches with too few CTAs split the keys of a
+// query tile over several CTAs and merge the partial results.
 int launch_attention_bf16(const bf16* qkv, int B, int T, int NH, int Tc, bf16* out_c, bf16* out_x,
-                          float scale, int* dev_status, cudaStream_t stream, int out_e4m3 = 0);
+                          float scale, int* dev_status, cudaStream_t stream, int out_e4m3 = 0,
+                          void* scratch = nullptr, size_t scratch_bytes = 0);
+size_t attention_scratch_bytes(int B, int T, int NH);
 
 // Generic SIMT attention (any head_dim <= 128, fp32 or bf16 in, fp32 math).
 // q: row (b*T + t) at base + row*ld + h*D; k, v: row (b*L + j) at base + row*ldk + h*D

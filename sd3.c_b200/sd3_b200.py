@@ -64,6 +64,8 @@ PROTOTYPES = {
     "sd3_qkv_project": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "sd3_qkv_project_groups": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "sd3_attention": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p]),
+    "sd3_attention_scratch_bytes": (c_long, [c_int, c_int, c_int]),
+    "sd3_attention_ws": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_long, c_void_p]),
     "sd3_attention_generic": (c_int, [c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_long, c_int, c_float, c_void_p]),
     "sd3_cross_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_long, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_long, c_int, c_float, c_void_p]),
     "sd3_conv2d": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
@@ -220,14 +222,28 @@ def qkv_project_groups(x_bf16, w_nk_bf16, bias, wq, wk, eps, out, E_out, head_gr
     return out
 
 
-def attention(qkv_bf16, B, T, num_heads, Tc, scale, want_context=True):
+def attention(qkv_bf16, B, T, num_heads, Tc, scale, want_context=True, scratch=None):
+    """scratch: optional uint8/float tensor of sd3_attention_scratch_bytes(B, T, num_heads) bytes;
+    with it, shapes that would not fill the GPU split the keys over several CTAs."""
     torch = _torch()
     E = num_heads * 64
     out_c = torch.empty((B, Tc, E), device=qkv_bf16.device, dtype=torch.bfloat16) if (want_context and Tc > 0) else None
     out_x = torch.empty((B, T - Tc, E), device=qkv_bf16.device, dtype=torch.bfloat16)
-    check(lib().sd3_attention(ptr(qkv_bf16), B, T, num_heads, Tc, ptr(out_c), ptr(out_x), scale,
-                              stream_ptr()), "sd3_attention")
+    if scratch is None:
+        check(lib().sd3_attention(ptr(qkv_bf16), B, T, num_heads, Tc, ptr(out_c), ptr(out_x), scale,
+                                  stream_ptr()), "sd3_attention")
+    else:
+        check(lib().sd3_attention_ws(ptr(qkv_bf16), B, T, num_heads, Tc, ptr(out_c), ptr(out_x), scale,
+                                     ptr(scratch), scratch.numel() * scratch.element_size(), stream_ptr()),
+              "sd3_attention_ws")
     return out_c, out_x
+
+
+def attention_scratch(B, T, num_heads, device="cuda"):
+    """Scratch tensor for attention(..., scratch=...) / sd3_attention_ws, or None if this shape
+    fills the GPU without a key split."""
+    n = lib().sd3_attention_scratch_bytes(B, T, num_heads)
+    return _torch().empty(n, device=device, dtype=_torch().uint8) if n > 0 else None
 
 
 def attention_generic(q, k, v, num_heads, scale=None, out_dtype=None):

@@ -189,6 +189,10 @@ class PackedModel:
                  att2=e(1, P * Tl, 3 * Eh), o_c=e(1, Tc, Eh), o_x=e(1, P * Tl, Eh), recv_o=e(P, Tl, Eh),
                  o_rows=e(Tl, E), gath_c=e(P, Tc, Eh), o_ctx=e(Tc, E), hid_x=e(Tl, F), hid_c=e(Tc, F),
                  mod=torch.empty((1, self.ada_total), device=dev, dtype=torch.float32))
+        NHl = self.cfg["attn_heads"] // P
+        sc1 = self.sd3.attention_scratch(1, Tc + P * Tl, NHl)
+        sc2 = self.sd3.attention_scratch(1, P * Tl, NHl)
+        b["attn_scratch"] = sc1 if (sc2 is None or (sc1 is not None and sc1.numel() >= sc2.numel())) else sc2
         self.ws[key] = b
         return b
 
@@ -216,9 +220,13 @@ def _linear_into(sd3, x, w, b, out, act=0):
     return out
 
 
-def _attention_into(sd3, att_in, T, heads, Tc, scale, o_c, o_x):
-    sd3.check(sd3.lib().sd3_attention(sd3.ptr(att_in), 1, T, heads, Tc, sd3.ptr(o_c) if o_c is not None else None,
-                                      sd3.ptr(o_x), scale, sd3.stream_ptr()), "sd3_attention")
+def _attention_into(sd3, att_in, T, heads, Tc, scale, o_c, o_x, scratch=None):
+    """Attention over the local heads.  With few heads per rank a launch has too few CTAs for
+    the GPU; the scratch buffer lets the kernel split the keys of each query tile."""
+    sd3.check(sd3.lib().sd3_attention_ws(sd3.ptr(att_in), 1, T, heads, Tc, sd3.ptr(o_c) if o_c is not None else None,
+                                         sd3.ptr(o_x), scale, sd3.ptr(scratch),
+                                         scratch.numel() * scratch.element_size() if scratch is not None else 0,
+                                         sd3.stream_ptr()), "sd3_attention_ws")
 
 
 def block_forward(pm, l, mod, c, x_loc, comm, last, dual):
@@ -272,7 +280,7 @@ def block_forward(pm, l, mod, c, x_loc, comm, last, dual):
     wq, wk = rms("latent")
     sd3.qkv_project_groups(B["h_x"], w, b, wq, wk, 1e-6, B["send"], E, P)
     comm.all_to_all_into(att_in[0, Tc:], B["send"])
-    _attention_into(sd3, att_in, Tc + Tx, NH // P, Tc, scale, None if last else B["o_c"], B["o_x"])
+    _attention_into(sd3, att_in, Tc + Tx, NH // P, Tc, scale, None if last else B["o_c"], B["o_x"], B["attn_scratch"])
     comm.all_to_all_into(B["recv_o"], B["o_x"])
     B["o_rows"].view(Tl, P, Eh).copy_(B["recv_o"].permute(1, 0, 2))
     if not last:
@@ -288,7 +296,7 @@ def block_forward(pm, l, mod, c, x_loc, comm, last, dual):
         wq, wk = rms("latent_dual")
         sd3.qkv_project_groups(B["h_x2"], w, b, wq, wk, 1e-6, B["send"], E, P)
         comm.all_to_all_into(B["att2"][0], B["send"])
-        _attention_into(sd3, B["att2"], Tx, NH // P, 0, scale, None, B["o_x"])
+        _attention_into(sd3, B["att2"], Tx, NH // P, 0, scale, None, B["o_x"], B["attn_scratch"])
         comm.all_to_all_into(B["recv_o"], B["o_x"])
         B["o_rows"].view(Tl, P, Eh).copy_(B["recv_o"].permute(1, 0, 2))
         w, b = pm.lin(pre + "latent_dual_attn_Wout")

@@ -293,3 +293,27 @@ def test_attention_rising_scores_rescale_every_sub_tile(sd3):
     assert torch.isfinite(ox.float()).all()
     assert rel_l2(ox, ref) < 1e-2
     assert sd3.device_status() == 0
+
+
+@pytest.mark.parametrize("B,T,NH,Tc,amp", [(1, 4429, 3, 333, 1.0), (1, 2100, 2, 0, 4.0), (1, 16717, 3, 333, 1.0),
+                                           (2, 2500, 1, 77, 1.0)])
+def test_attention_key_split_matches_unsplit(sd3, B, T, NH, Tc, amp):
+    """sd3_attention_ws: launches with too few CTAs for the GPU split the keys of each query
+    tile over several CTAs and merge (maximum, row sum, unnormalised rows); same result as the
+    one-CTA-per-tile path and as the fp32 reference."""
+    torch.manual_seed(T + NH)
+    E = NH * 64
+    qkv = (torch.randn(B, T, 3 * E, device="cuda") * amp).bfloat16()
+    scratch = sd3.attention_scratch(B, T, NH)
+    assert scratch is not None  # these shapes are chosen to need the split
+    oc0, ox0 = sd3.attention(qkv, B, T, NH, Tc, 0.125)
+    oc1, ox1 = sd3.attention(qkv, B, T, NH, Tc, 0.125, scratch=scratch)
+    torch.cuda.synchronize()
+    assert sd3.device_status() == 0
+    q, k, v = [t.view(B, T, NH, 64).transpose(1, 2).float() for t in qkv.chunk(3, -1)]
+    ref = torch.nn.functional.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, T, E)
+    got = torch.cat([oc1, ox1], 1) if oc1 is not None else ox1
+    assert rel_l2(got, ref) < 1e-2
+    assert rel_l2(ox1, ox0) < 5e-3  # the two paths differ by bf16 rounding of differently ordered sums
+    # a shape that fills the GPU needs no scratch, and a null scratch falls back to the unsplit path
+    assert sd3.attention_scratch(8, 4429, 24) is None
