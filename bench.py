@@ -198,12 +198,15 @@ def kernel_breakdown(torch, s, peaks):
     gemm_case("gemm_tcgen05 mlp1 x (GELU-tanh)", Mx, FH, E, 24, "gelu")
     gemm_case("gemm_tcgen05 mlp2 x (gate+residual)", Mx, E, FH, 24, "gate")
 
-    def attn_case(name, Tn, Tc, count):
-        qkv = torch.randn(B, Tn, 3 * E, device=dev).bfloat16()
+    def attn_case(name, Tn, Tc, count, bounded=True):
+        qkv = normed_qkv(torch, B, Tn, dev)
         oc = torch.empty(B, max(Tc, 1), E, device=dev, dtype=torch.bfloat16)
         ox = torch.empty(B, Tn - Tc, E, device=dev, dtype=torch.bfloat16)
-        fn = lambda: s.check(s.lib().sd3_attention(s.ptr(qkv), B, Tn, NH, Tc, s.ptr(oc) if Tc else None,
-                                                   s.ptr(ox), 0.125, s.stream_ptr()))
+        # the step's launches: q and k are RMS-normed by the QKV epilogue (weights 1 in this random-init
+        # model), the engine passes the bound that follows from the norm weights
+        bound = QK_SCORE_BOUND if bounded else 0.0
+        fn = lambda: s.check(s.lib().sd3_attention_bounded(s.ptr(qkv), B, Tn, NH, Tc, s.ptr(oc) if Tc else None,
+                                                           s.ptr(ox), 0.125, bound, None, 0, s.stream_ptr()))
         ms = time_events(torch, fn, 5)
         fl = 4.0 * B * NH * Tn * Tn * 64
         d = dict(kernel=name, launches_per_step=count, ms=round(ms, 4), achieved=round(fl / ms / 1e9, 1),
@@ -211,8 +214,9 @@ def kernel_breakdown(torch, s, peaks):
         out.append(d)
         return d
 
-    joint = attn_case("attention_tcgen05 joint T=4429", T, TC, 24)
-    attn_case("attention_tcgen05 image-only T=4096", TX, 0, 13)
+    joint = attn_case("attention_tcgen05 joint T=4429 (bounded scores, as in the step)", T, TC, 24)
+    attn_case("attention_tcgen05 image-only T=4096 (bounded scores, as in the step)", TX, 0, 13)
+    attn_case("attention_tcgen05 joint T=4429, online softmax (no bound given)", T, TC, 0, bounded=False)
 
     x = torch.randn(Mx, E, device=dev)
     mod = torch.randn(B, 9 * E, device=dev)
@@ -297,11 +301,11 @@ def profile_case(name, reps=3):
             fn = lambda: s.check(s.lib().sd3_linear(s.ptr(x), s.ptr(w), s.ptr(bias), s.ptr(o), 1, M, N, K, act, s.stream_ptr()))
     elif name in ("attn_joint", "attn_self"):
         Tn, Tc = (T, TC) if name == "attn_joint" else (TX, 0)
-        qkv = torch.randn(Bp, Tn, 3 * E, device=dev).bfloat16()
+        qkv = normed_qkv(torch, Bp, Tn, dev)
         oc = torch.empty(Bp, max(Tc, 1), E, device=dev, dtype=torch.bfloat16)
         ox = torch.empty(Bp, Tn - Tc, E, device=dev, dtype=torch.bfloat16)
-        fn = lambda: s.check(s.lib().sd3_attention(s.ptr(qkv), Bp, Tn, NH, Tc, s.ptr(oc) if Tc else None,
-                                                   s.ptr(ox), 0.125, s.stream_ptr()))
+        fn = lambda: s.check(s.lib().sd3_attention_bounded(s.ptr(qkv), Bp, Tn, NH, Tc, s.ptr(oc) if Tc else None,
+                                                           s.ptr(ox), 0.125, QK_SCORE_BOUND, None, 0, s.stream_ptr()))
     elif name == "ln_mod":
         Bl = 8
         x = torch.randn(Bl * TX, E, device=dev)
@@ -433,6 +437,18 @@ def run_reference(args):
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": cpu.kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
+
+
+# |q . k| <= 64 max|wq| max|wk| after the per-head RMSNorm; the benchmark model's norm weights are 1
+QK_SCORE_BOUND = 1.01 * 64.0
+
+
+def normed_qkv(torch, batch, tokens, dev):
+    """Packed (batch, tokens, 3E) bf16 attention input as the QKV epilogue leaves it: q and k
+    RMS-normed per head (weights 1), v random."""
+    raw = torch.randn(batch, tokens, 3, NH, 64, device=dev)
+    raw[:, :, :2] *= torch.rsqrt(raw[:, :, :2].pow(2).mean(-1, keepdim=True) + 1e-6)
+    return raw.reshape(batch, tokens, 3 * E).bfloat16()
 
 
 def library_attention_rows(torch, peaks):

@@ -144,6 +144,19 @@ SD3_API long sd3_attention_scratch_bytes(int B, int T, int num_heads);
 SD3_API int sd3_attention_ws(const void* qkv_bf16, int B, int T, int num_heads, int Tc, void* out_c_bf16,
                              void* out_x_bf16, float scale, void* scratch, long scratch_bytes, void* stream);
 
+/* sd3_attention_ws for callers that know an upper bound on |q . k| over every query and key of
+ * the call (score_bound, in raw dot-product units; 0 = unknown).  After the q/k RMSNorm of the
+ * model (module_tests/modules.py:286-297) every head vector has norm at most
+ * sqrt(head_dim) * max|weight|, so score_bound = 64 * max|wq| * max|wk| (times 1.01 for the
+ * bf16 rounding of q and k) holds for any input.  If score_bound * scale * log2(e) <= 80, the
+ * softmax is evaluated as 2^(s c) / sum 2^(s c) without a running maximum -- identical in exact
+ * arithmetic, no overflow or underflow possible within the bound, fewer instructions per score;
+ * otherwise, and for score_bound <= 0, this is sd3_attention_ws.  A bound that does not hold
+ * gives undefined results (inf / NaN), never a device fault.  scratch may be null. */
+SD3_API int sd3_attention_bounded(const void* qkv_bf16, int B, int T, int num_heads, int Tc, void* out_c_bf16,
+                                  void* out_x_bf16, float scale, float score_bound, void* scratch,
+                                  long scratch_bytes, void* stream);
+
 /* Generic attention in fp32 arithmetic for any head_dim <= 128: q, k, v are
  * (B, Tq|Tk, num_heads*head_dim) row-major with leading dimension ld elements,
  * dtype in_dtype; out (B, Tq, num_heads*head_dim) of out_dtype.  Stand-in for

@@ -220,6 +220,13 @@ int sd3_attention_ws(const void* qkv, int B, int T, int num_heads, int Tc, void*
                                scratch_bytes > 0 ? static_cast<size_t>(scratch_bytes) : 0);
 }
 
+int sd3_attention_bounded(const void* qkv, int B, int T, int num_heads, int Tc, void* out_c, void* out_x,
+                          float scale, float score_bound, void* scratch, long scratch_bytes, void* stream) {
+  return launch_attention_bf16(static_cast<const bf16*>(qkv), B, T, num_heads, Tc, static_cast<bf16*>(out_c),
+                               static_cast<bf16*>(out_x), scale, device_status_word(), S(stream), 0, scratch,
+                               scratch_bytes > 0 ? static_cast<size_t>(scratch_bytes) : 0, score_bound);
+}
+
 int sd3_attention_generic(const void* q, const void* k, const void* v, long ld, int in_dtype,
                           int B, int T, int num_heads, int head_dim, void* out, long ldo,
                           int out_dtype, float scale, void* stream) {

@@ -44,6 +44,7 @@
 // rows straight into the context and image output buffers.
 #include <cuda.h>
 
+#include <cmath>
 #include <mutex>
 
 #include "kernels.h"
@@ -69,6 +70,8 @@ constexpr int AT_S_COL = 0;     // scores of one 128-key tile: 128 fp32 columns
 constexpr int AT_P_COL = 128;   // exp2 of the scores as bf16 pairs: 64 columns (keys 2c, 2c+1 in column c)
 constexpr int AT_O_COL = 192;   // O: 64 fp32 columns
 constexpr int AT_POLY_EVERY = 4;  // of every 4 pairs of exponentials, one element goes to the FMA pipe
+constexpr int AT_POLY_PAIRS = 0x49;  // bounded mode: pairs 0, 3 and 6 of every 8 go to the FMA pipe whole
+constexpr float AT_BOUND_MAX = 80.0f;  // largest |score| scale log2(e) the bounded mode accepts
 constexpr int AT_SMEM_BYTES = (1 + 2 * AT_STAGES) * AT_TILE_BYTES + 256 + 1024;
 
 struct AttnArgs {
@@ -194,6 +197,53 @@ __device__ __forceinline__ void exp_pack(uint32_t (&r)[32], float c, float nmc, 
   }
 }
 
+// 2^(s c) for a pair of scores on the FMA pipe with packed f32x2 instructions: n = round(s c)
+// by the magic-number add, f = s c - n in [-0.5, 0.5], the same degree-3 polynomial, exponent
+// added as an integer.  Needs |s c| < 2^22 and a finite result (the bounded mode guarantees
+// |s c| <= AT_BOUND_MAX); six packed FMAs and two integer operations per pair.
+__device__ __forceinline__ float2 ex2_poly2(float2 s, float2 c2) {
+  const float2 magic = make_float2(12582912.0f, 12582912.0f);
+  const float2 t = __ffma2_rn(s, c2, magic);
+  const float2 nn = __ffma2_rn(t, make_float2(-1.0f, -1.0f), magic);  // -round(s c)
+  const float2 f = __ffma2_rn(s, c2, nn);
+  float2 p = __ffma2_rn(f, make_float2(0.0558011f, 0.0558011f), make_float2(0.2402265f, 0.2402265f));
+  p = __ffma2_rn(p, f, make_float2(0.6931472f, 0.6931472f));
+  p = __ffma2_rn(p, f, make_float2(1.0f, 1.0f));
+  p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+  p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
+  return p;
+}
+
+// Bounded mode: r[i] = bf16x2(2^(r[2i] c), 2^(r[2i+1] c)) for i < 16, in place, no maximum
+// subtracted; the exponentials are added into acc.  POLY: three pairs of every eight go to the
+// FMA pipe (a microbenchmark of this loop: 7.2 clk per warp-wide element against 8.2 with every
+// exponential on the MUFU unit; 2/8 the same, 4/8 slower).  Without POLY a score of -inf (a
+// masked key) gives exactly 0.
+template <bool POLY>
+__device__ __forceinline__ void exp2_pack(uint32_t (&r)[32], float c, float2& acc) {
+  const float2 c2 = make_float2(c, c);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float2 s = make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+    float2 p;
+    if (POLY && ((AT_POLY_PAIRS >> (i % 8)) & 1)) {
+      p = ex2_poly2(s, c2);
+    } else {
+      const float2 x = __fmul2_rn(s, c2);
+      p.x = ex2_approx(x.x);
+      p.y = ex2_approx(x.y);
+    }
+    acc = __fadd2_rn(acc, p);
+    r[i] = pack_bf16x2(p.x, p.y);
+  }
+}
+
+// BOUNDED: the caller guarantees |q . k| scale log2(e) <= AT_BOUND_MAX for every query and key
+// (the engine derives it from the RMSNorm weights of q and k), so 2^(s c) can neither overflow
+// nor vanish in fp32 / bf16 and the softmax needs no running maximum: no row maximum, no vote,
+// no rescaling of O; P = 2^(s c) and the row sum normalise the output exactly as before
+// (softmax is invariant to the subtracted constant).
+template <bool BOUNDED>
 __global__ void __launch_bounds__(AT_THREADS, 2)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -312,7 +362,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
     const uint32_t p_tmem = lane_base + AT_P_COL;
     const uint32_t o_tmem = lane_base + AT_O_COL;
     const float c = a.scale_log2e;
-    float m_used = -INFINITY;  // running max (raw score units) the exponentials refer to
+    float m_used = BOUNDED ? 0.0f : -INFINITY;  // running max (raw score units) the exponentials refer to
     float2 l2 = make_float2(0.f, 0.f);
     bool ok = true;
     uint32_t pre_s = 0;  // early test of s_full for the coming tile
@@ -357,7 +407,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
       tmem_ld_32x32b_x32(s_tmem + 32, rb);
       tmem_wait_ld();
       if (ragged) { mask_cols(ra, kv0, T); mask_cols(rb, kv0 + 32, T); }
-      half_step(ra, rb, false);
+      if (BOUNDED) {
+        if (ragged) { exp2_pack<false>(ra, c, l2); exp2_pack<false>(rb, c, l2); }
+        else { exp2_pack<true>(ra, c, l2); exp2_pack<true>(rb, c, l2); }
+      } else {
+        half_step(ra, rb, false);
+      }
       // the second half is only loaded now: with all 128 scores live the kernel spills
       tmem_ld_32x32b_x32(s_tmem + 64, rc);
       tmem_ld_32x32b_x32(s_tmem + 96, rd);
@@ -367,7 +422,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
       if (ragged) { mask_cols(rc, kv0 + 64, T); mask_cols(rd, kv0 + 96, T); }
       uint32_t pre_pv = 1;
       if (j >= 1) pre_pv = mbar_test_wait(&pv_done[stp], parp);
-      half_step(rc, rd, true);
+      if (BOUNDED) {
+        if (ragged) { exp2_pack<false>(rc, c, l2); exp2_pack<false>(rd, c, l2); }
+        else { exp2_pack<true>(rc, c, l2); exp2_pack<true>(rd, c, l2); }
+      } else {
+        half_step(rc, rd, true);
+      }
       // P is free once the products of the previous tile are complete (tested half a tile ago)
       if (j >= 1 && ok) ok = mbar_wait_pre(pre_pv, &pv_done[stp], parp, wc, DEV_TIMEOUT_ATTN_O);
       if (!ok) break;
@@ -544,9 +604,12 @@ size_t attention_scratch_bytes(int B, int T, int NH) {
   return sp > 1 ? static_cast<size_t>(B) * NH * sp * T * (AT_D + 2) * sizeof(float) : 0;
 }
 
+// score_bound: an upper bound on |q . k| over every query and key of the launch, or 0 when none
+// is known.  With 0 < score_bound * scale * log2(e) <= 80 the softmax runs without a running
+// maximum (same result, about 8 % faster); any other value selects the online softmax.
 int launch_attention_bf16(const bf16* qkv, int B, int T, int NH, int Tc, bf16* out_c, bf16* out_x,
                           float scale, int* dev_status, cudaStream_t stream, int out_e4m3, void* scratch,
-                          size_t scratch_bytes) {
+                          size_t scratch_bytes, float score_bound) {
   if (!qkv || !out_x || B <= 0 || T <= 0 || NH <= 0 || Tc < 0 || Tc > T ||
       (reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(out_x) & 15) ||
       (reinterpret_cast<uintptr_t>(out_c) & 15)) {
@@ -569,8 +632,11 @@ int launch_attention_bf16(const bf16* qkv, int B, int T, int NH, int Tc, bf16* o
   if (dev >= 0 && dev < 64) {
     std::lock_guard<std::mutex> lock(attr_mutex);
     if (!attr_done[dev]) {
-      cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel,
+      cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<false>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES);
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(attention_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 AT_SMEM_BYTES);
       if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(attention)");
       attr_done[dev] = true;
     }
@@ -595,7 +661,11 @@ int launch_attention_bf16(const bf16* qkv, int B, int T, int NH, int Tc, bf16* o
     }
   }
   const dim3 grid(qtiles * a.kv_split, NH, B);
-  attention_tcgen05_kernel<<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(tm, a);
+  const float bound_log2 = score_bound * fabsf(a.scale_log2e);
+  if (score_bound > 0.0f && bound_log2 <= AT_BOUND_MAX)
+    attention_tcgen05_kernel<true><<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(tm, a);
+  else
+    attention_tcgen05_kernel<false><<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(tm, a);
   int lrc = after_launch("attention_tcgen05_kernel");
   if (lrc || a.kv_split == 1) return lrc;
   const long warps = static_cast<long>(B) * NH * T;

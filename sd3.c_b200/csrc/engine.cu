@@ -17,6 +17,8 @@
 //   [dual] QKV GEMM(x2), attention over image tokens, out-proj GEMM with gate2
 //   LN+modulate(x), MLP1 GEMM (+GELU-tanh), MLP2 GEMM (+gate, +residual); same for c
 #include <math.h>
+#include <algorithm>
+#include <cmath>
 #include <string.h>
 
 #include <map>
@@ -48,6 +50,9 @@ struct LayerW {
   Linear d_qkv, d_out;
   float *c_wq = nullptr, *c_wk = nullptr, *x_wq = nullptr, *x_wk = nullptr, *d_wq = nullptr,
         *d_wk = nullptr;
+  // upper bounds on |q . k| of the joint and the image-only attention, from the RMSNorm weights of
+  // q and k (0: none, the attention keeps its running maximum); set by sd3_model_finalize
+  float joint_bound = 0.f, dual_bound = 0.f;
   long c_mod_off = 0, x_mod_off = 0;  // column offsets into the concatenated AdaLN output
   int c_chunks = 0, x_chunks = 0;
   bool dual = false, last = false;
@@ -370,13 +375,13 @@ int run_qkv(sd3_model* m, const Linear& L, const void* h, void* qkv, int B, int 
 
 // out_e4m3 (FP8 mode, head_dim 64 only): the outputs feed FP8 out-projections
 int run_attention(sd3_model* m, const void* qkv, int B, int T, int Tc, void* o_c, void* o_x,
-                  cudaStream_t st, bool out_e4m3 = false) {
+                  cudaStream_t st, bool out_e4m3 = false, float score_bound = 0.f) {
   const float scale = 1.0f / sqrtf(static_cast<float>(m->D));
   if (!m->f32 && m->D == 64)
     return launch_attention_bf16(static_cast<const bf16*>(qkv), B, T, m->NH, Tc,
                                  static_cast<bf16*>(o_c), static_cast<bf16*>(o_x), scale, m->status,
                                  st, out_e4m3 ? 1 : 0, m->ws.attn_scratch_bytes ? m->ws.attn_scratch : nullptr,
-                                 m->ws.attn_scratch_bytes);
+                                 m->ws.attn_scratch_bytes, score_bound);
   if (out_e4m3) {
     set_last_error("e4m3 attention output needs head_dim 64");
     return ST_UNSUPPORTED;
@@ -477,7 +482,7 @@ int block_body(sd3_model* m, int l, float* c, float* x, int B, int Tc, int Tx, c
   // FP8 mode: both out-projections of the joint attention must take e4m3 for the
   // kernel to write it (one flag for both outputs)
   const bool o8 = m->fp8 && m->D == 64 && L.x_out.w8 && (L.last || L.c_out.w8);
-  SD3_TRY(run_attention(m, w.qkv, B, T, Tc, L.last ? nullptr : w.o_c, w.o_x, st, o8));
+  SD3_TRY(run_attention(m, w.qkv, B, T, Tc, L.last ? nullptr : w.o_c, w.o_x, st, o8, L.joint_bound));
   if (grouped && !L.last) {
     SD3_TRY(run_linear_pair(m, L.x_out, w.o_x, B * Tx, gate_epilogue(L.x_out, Tx, x_gate_a, ms, x), o8,
                             L.c_out, w.o_c, B * Tc, gate_epilogue(L.c_out, Tc, c_gate_a, ms, c), o8, st));
@@ -488,7 +493,7 @@ int block_body(sd3_model* m, int l, float* c, float* x, int B, int Tc, int Tx, c
   if (L.dual) {
     SD3_TRY(run_qkv(m, L.d_qkv, w.h_x2, w.qkv2, B, Tx, Tx, 0, L.d_wq, L.d_wk, st, x8a));
     const bool o8d = m->fp8 && m->D == 64 && L.d_out.w8;
-    SD3_TRY(run_attention(m, w.qkv2, B, Tx, 0, nullptr, w.o_x2, st, o8d));
+    SD3_TRY(run_attention(m, w.qkv2, B, Tx, 0, nullptr, w.o_x2, st, o8d, L.dual_bound));
     SD3_TRY(run_gate_resid(m, L.d_out, w.o_x2, B, Tx, x_gate_2, ms, x, st, o8d));
   }
   // MLPs of both streams: LayerNorm + modulate each, then the two first linears (GELU-tanh) and
@@ -553,6 +558,38 @@ int quantize_block_weights(sd3_model* m) {
     }
   }
   return check_cuda(cudaDeviceSynchronize(), "quantize weights");
+}
+
+// After the per-head RMSNorm (module_tests/modules.py:286-297: x / sqrt(mean(x^2) + eps) * w) a
+// head vector has norm at most sqrt(D) max|w|, whatever the input; so |q . k| <= D max|wq| max|wk|
+// for every query and key of an attention.  1 % on top covers the bf16 rounding of q and k.
+int compute_score_bounds(sd3_model* m) {
+  for (LayerW& L : m->layers) L.joint_bound = L.dual_bound = 0.f;
+  if (!m->cfg.use_qk_norm || m->f32 || m->D != 64) return ST_OK;
+  int rc = check_cuda(cudaDeviceSynchronize(), "parameter copies");
+  if (rc) return rc;
+  std::vector<float> h(m->D);
+  bool ok = true;
+  auto amax = [&](const float* w) {
+    if (!w || cudaMemcpy(h.data(), w, sizeof(float) * m->D, cudaMemcpyDeviceToHost) != cudaSuccess) {
+      ok = false;
+      return 0.f;
+    }
+    float a = 0.f;
+    for (float v : h) a = std::max(a, std::fabs(v));
+    return std::isfinite(a) ? a : (ok = false, 0.f);
+  };
+  for (LayerW& L : m->layers) {
+    ok = true;
+    const float q = std::max(amax(L.c_wq), amax(L.x_wq)), k = std::max(amax(L.c_wk), amax(L.x_wk));
+    if (ok) L.joint_bound = 1.01f * m->D * q * k;
+    if (L.dual) {
+      ok = true;
+      const float q2 = amax(L.d_wq), k2 = amax(L.d_wk);
+      if (ok) L.dual_bound = 1.01f * m->D * q2 * k2;
+    }
+  }
+  return ST_OK;
 }
 
 }  // namespace
@@ -725,6 +762,10 @@ int sd3_model_finalize(sd3_model* m, int* missing) {
   }
   if (m->fp8 && !m->finalized) {
     int rc = quantize_block_weights(m);
+    if (rc) return rc;
+  }
+  if (!m->finalized) {
+    int rc = compute_score_bounds(m);
     if (rc) return rc;
   }
   m->finalized = true;

@@ -108,10 +108,12 @@ int launch_gemm_grouped(const GemmProblem& a, const GemmProblem& b, int operand_
 // out_e4m3: out_c / out_x receive one e4m3 byte per element (rows E bytes apart) instead of bf16.
 // scratch (optional, 16-byte aligned, attention_scratch_bytes(B, T, NH) bytes, which is 0 for
 // shapes that fill the machine anyway): lets launches with too few CTAs split the keys of a
-// query tile over several CTAs and merge the partial results.
+// query tile over several CTAs and merge the partial results.  score_bound (optional): an upper
+// bound on |q . k| for every query and key, 0 if unknown; a bound of at most 80 / (scale log2 e)
+// lets the softmax run without a running maximum.
 int launch_attention_bf16(const bf16* qkv, int B, int T, int NH, int Tc, bf16* out_c, bf16* out_x,
                           float scale, int* dev_status, cudaStream_t stream, int out_e4m3 = 0,
-                          void* scratch = nullptr, size_t scratch_bytes = 0);
+                          void* scratch = nullptr, size_t scratch_bytes = 0, float score_bound = 0.0f);
 size_t attention_scratch_bytes(int B, int T, int NH);
 
 // Generic SIMT attention (any head_dim <= 128, fp32 or bf16 in, fp32 math).

@@ -66,6 +66,7 @@ PROTOTYPES = {
     "sd3_attention": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p]),
     "sd3_attention_scratch_bytes": (c_long, [c_int, c_int, c_int]),
     "sd3_attention_ws": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_long, c_void_p]),
+    "sd3_attention_bounded": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p, c_long, c_void_p]),
     "sd3_attention_generic": (c_int, [c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_long, c_int, c_float, c_void_p]),
     "sd3_cross_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_long, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_long, c_int, c_float, c_void_p]),
     "sd3_conv2d": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
@@ -222,14 +223,29 @@ def qkv_project_groups(x_bf16, w_nk_bf16, bias, wq, wk, eps, out, E_out, head_gr
     return out
 
 
-def attention(qkv_bf16, B, T, num_heads, Tc, scale, want_context=True, scratch=None):
+def qk_norm_score_bound(wq, wk, head_dim=64):
+    """Upper bound on |q . k| after the per-head RMSNorm with weights wq, wk (tensors, or lists of
+    tensors when several norms feed one attention): every normed head vector has norm at most
+    sqrt(head_dim) * max|w|; 1 % on top for the bf16 rounding of q and k."""
+    def amax(w):
+        ws = w if isinstance(w, (list, tuple)) else [w]
+        return max(float(t.detach().abs().max()) for t in ws)
+    return 1.01 * head_dim * amax(wq) * amax(wk)
+
+
+def attention(qkv_bf16, B, T, num_heads, Tc, scale, want_context=True, scratch=None, score_bound=0.0):
     """scratch: optional uint8/float tensor of sd3_attention_scratch_bytes(B, T, num_heads) bytes;
-    with it, shapes that would not fill the GPU split the keys over several CTAs."""
+    with it, shapes that would not fill the GPU split the keys over several CTAs.
+    score_bound: optional upper bound on |q . k| (see qk_norm_score_bound, sd3_attention_bounded)."""
     torch = _torch()
     E = num_heads * 64
     out_c = torch.empty((B, Tc, E), device=qkv_bf16.device, dtype=torch.bfloat16) if (want_context and Tc > 0) else None
     out_x = torch.empty((B, T - Tc, E), device=qkv_bf16.device, dtype=torch.bfloat16)
-    if scratch is None:
+    if score_bound > 0.0:
+        nbytes = scratch.numel() * scratch.element_size() if scratch is not None else 0
+        check(lib().sd3_attention_bounded(ptr(qkv_bf16), B, T, num_heads, Tc, ptr(out_c), ptr(out_x), scale,
+                                          score_bound, ptr(scratch), nbytes, stream_ptr()), "sd3_attention_bounded")
+    elif scratch is None:
         check(lib().sd3_attention(ptr(qkv_bf16), B, T, num_heads, Tc, ptr(out_c), ptr(out_x), scale,
                                   stream_ptr()), "sd3_attention")
     else:

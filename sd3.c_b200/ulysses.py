@@ -151,6 +151,19 @@ class PackedModel:
         self.ada_w = torch.cat(ws, 0).contiguous()
         self.ada_b = torch.cat(bs, 0).contiguous()
         self.ada_total = off
+        # bounds on |q . k| of each block's joint and image-only attention, from the q/k RMSNorm
+        # weights (0.0: no norm, the attention keeps its running maximum)
+        self.score_bound = {}
+        for l in range(L):
+            pre = "transformer.%d." % l
+            def norms(kind, streams):
+                return [self.w[pre + s_ + "_rmsnorm_" + kind + ".weight"] for s_ in streams
+                        if pre + s_ + "_rmsnorm_" + kind + ".weight" in self.w]
+            q, k = norms("query", ("context", "latent")), norms("key", ("context", "latent"))
+            joint = sd3.qk_norm_score_bound(q, k) if len(q) == 2 and len(k) == 2 else 0.0
+            q2, k2 = norms("query", ("latent_dual",)), norms("key", ("latent_dual",))
+            dual = sd3.qk_norm_score_bound(q2, k2) if q2 and k2 else 0.0
+            self.score_bound[l] = (joint, dual)
         self.local = None
         self.ws = {}
         torch.cuda.synchronize()
@@ -220,13 +233,15 @@ def _linear_into(sd3, x, w, b, out, act=0):
     return out
 
 
-def _attention_into(sd3, att_in, T, heads, Tc, scale, o_c, o_x, scratch=None):
+def _attention_into(sd3, att_in, T, heads, Tc, scale, o_c, o_x, scratch=None, score_bound=0.0):
     """Attention over the local heads.  With few heads per rank a launch has too few CTAs for
-    the GPU; the scratch buffer lets the kernel split the keys of each query tile."""
-    sd3.check(sd3.lib().sd3_attention_ws(sd3.ptr(att_in), 1, T, heads, Tc, sd3.ptr(o_c) if o_c is not None else None,
-                                         sd3.ptr(o_x), scale, sd3.ptr(scratch),
-                                         scratch.numel() * scratch.element_size() if scratch is not None else 0,
-                                         sd3.stream_ptr()), "sd3_attention_ws")
+    the GPU; the scratch buffer lets the kernel split the keys of each query tile.  score_bound:
+    the block's bound on |q . k| (0.0 if unknown)."""
+    sd3.check(sd3.lib().sd3_attention_bounded(sd3.ptr(att_in), 1, T, heads, Tc,
+                                              sd3.ptr(o_c) if o_c is not None else None, sd3.ptr(o_x), scale,
+                                              score_bound, sd3.ptr(scratch),
+                                              scratch.numel() * scratch.element_size() if scratch is not None else 0,
+                                              sd3.stream_ptr()), "sd3_attention_bounded")
 
 
 def block_forward(pm, l, mod, c, x_loc, comm, last, dual):
@@ -280,7 +295,8 @@ def block_forward(pm, l, mod, c, x_loc, comm, last, dual):
     wq, wk = rms("latent")
     sd3.qkv_project_groups(B["h_x"], w, b, wq, wk, 1e-6, B["send"], E, P)
     comm.all_to_all_into(att_in[0, Tc:], B["send"])
-    _attention_into(sd3, att_in, Tc + Tx, NH // P, Tc, scale, None if last else B["o_c"], B["o_x"], B["attn_scratch"])
+    _attention_into(sd3, att_in, Tc + Tx, NH // P, Tc, scale, None if last else B["o_c"], B["o_x"], B["attn_scratch"],
+                    pm.score_bound[l][0])
     comm.all_to_all_into(B["recv_o"], B["o_x"])
     B["o_rows"].view(Tl, P, Eh).copy_(B["recv_o"].permute(1, 0, 2))
     if not last:
@@ -296,7 +312,7 @@ def block_forward(pm, l, mod, c, x_loc, comm, last, dual):
         wq, wk = rms("latent_dual")
         sd3.qkv_project_groups(B["h_x2"], w, b, wq, wk, 1e-6, B["send"], E, P)
         comm.all_to_all_into(B["att2"][0], B["send"])
-        _attention_into(sd3, B["att2"], Tx, NH // P, 0, scale, None, B["o_x"], B["attn_scratch"])
+        _attention_into(sd3, B["att2"], Tx, NH // P, 0, scale, None, B["o_x"], B["attn_scratch"], pm.score_bound[l][1])
         comm.all_to_all_into(B["recv_o"], B["o_x"])
         B["o_rows"].view(Tl, P, Eh).copy_(B["recv_o"].permute(1, 0, 2))
         w, b = pm.lin(pre + "latent_dual_attn_Wout")

@@ -317,3 +317,76 @@ def test_attention_key_split_matches_unsplit(sd3, B, T, NH, Tc, amp):
     assert rel_l2(ox1, ox0) < 5e-3  # the two paths differ by bf16 rounding of differently ordered sums
     # a shape that fills the GPU needs no scratch, and a null scratch falls back to the unsplit path
     assert sd3.attention_scratch(8, 4429, 24) is None
+
+
+def _normed_qkv(B, T, NH, wq, wk, seed, amp=1.0):
+    """q and k per-head RMS-normed with weights wq, wk (as the QKV epilogue leaves them), v random."""
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    raw = torch.randn(B, T, 3, NH, 64, device="cuda", generator=gen) * amp
+
+    def rms(t, w):
+        return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+
+    q, k, v = rms(raw[:, :, 0], wq), rms(raw[:, :, 1], wk), raw[:, :, 2]
+    return torch.stack([q, k, v], 2).reshape(B, T, 3 * NH * 64).bfloat16()
+
+
+@pytest.mark.parametrize("B,T,NH,Tc,wamp", [(2, 1357, 3, 333, 1.0), (1, 128, 1, 0, 1.0), (2, 129, 2, 65, 2.0),
+                                            (1, 640, 2, 0, 2.5), (2, 4429, 2, 333, 1.0), (1, 1, 1, 0, 1.0),
+                                            (3, 77, 4, 13, 0.3)])
+def test_attention_bounded_matches_online(sd3, B, T, NH, Tc, wamp):
+    """sd3_attention_bounded: with a valid bound on |q . k| the softmax runs without a running
+    maximum; same result as the online softmax and the fp32 reference, ragged last tiles and
+    context/image split included.  wamp 2.5 gives scores up to 64 * 6.25 / 8 * log2(e) = 72 in
+    the exp2 domain, near the 80 the mode accepts."""
+    gen = torch.Generator(device="cuda").manual_seed(T)
+    wq = wamp * (1.0 + 0.2 * torch.rand(64, device="cuda", generator=gen) - 0.2)
+    wk = wamp * (1.0 + 0.2 * torch.rand(64, device="cuda", generator=gen) - 0.2)
+    qkv = _normed_qkv(B, T, NH, wq, wk, seed=T + 1)
+    bound = sd3.qk_norm_score_bound(wq, wk)
+    assert bound * 0.125 * 1.4426950408889634 <= 80.0  # the bounded kernel really runs
+    oc0, ox0 = sd3.attention(qkv, B, T, NH, Tc, 0.125)
+    oc1, ox1 = sd3.attention(qkv, B, T, NH, Tc, 0.125, score_bound=bound)
+    torch.cuda.synchronize()
+    assert sd3.device_status() == 0
+    E = NH * 64
+    q, k, v = [t.view(B, T, NH, 64).transpose(1, 2).float() for t in qkv.chunk(3, -1)]
+    ref = torch.nn.functional.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, T, E)
+    got = torch.cat([oc1, ox1], 1) if oc1 is not None else ox1
+    assert torch.isfinite(got.float()).all()
+    assert rel_l2(got, ref) < 1e-2
+    assert rel_l2(ox1, ox0) < 6e-3
+    # the actual scores respect the bound the weights promise
+    assert (q @ k.transpose(-1, -2)).abs().max().item() <= bound
+
+
+def test_attention_bounded_with_key_split(sd3):
+    """Bounded softmax together with the key split: the partial results carry maximum 0."""
+    B, T, NH, Tc = 1, 4429, 3, 333
+    wq = torch.full((64,), 1.3, device="cuda")
+    wk = torch.full((64,), 0.9, device="cuda")
+    qkv = _normed_qkv(B, T, NH, wq, wk, seed=3)
+    scratch = sd3.attention_scratch(B, T, NH)
+    assert scratch is not None
+    bound = sd3.qk_norm_score_bound(wq, wk)
+    oc0, ox0 = sd3.attention(qkv, B, T, NH, Tc, 0.125)
+    oc1, ox1 = sd3.attention(qkv, B, T, NH, Tc, 0.125, scratch=scratch, score_bound=bound)
+    torch.cuda.synchronize()
+    assert sd3.device_status() == 0
+    assert rel_l2(ox1, ox0) < 6e-3 and rel_l2(oc1, oc0) < 6e-3
+
+
+def test_attention_bound_above_limit_uses_online_softmax(sd3):
+    """A bound above 80 / (scale log2 e), or none, selects the online softmax: large scores stay
+    finite (the bounded arithmetic would overflow on these inputs)."""
+    torch.manual_seed(5)
+    B, T, NH = 1, 700, 2
+    qkv = (torch.randn(B, T, 3 * NH * 64, device="cuda") * 6).bfloat16()
+    q, k, v = [t.view(B, T, NH, 64).transpose(1, 2).float() for t in qkv.chunk(3, -1)]
+    bound = (q @ k.transpose(-1, -2)).abs().max().item() * 1.01
+    assert bound * 0.125 * 1.4426950408889634 > 80.0
+    _, ox = sd3.attention(qkv, B, T, NH, 0, 0.125, score_bound=bound)
+    ref = torch.nn.functional.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, T, -1)
+    assert torch.isfinite(ox.float()).all()
+    assert rel_l2(ox, ref) < 2e-2
+    assert sd3.device_status() == 0
