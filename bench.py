@@ -199,14 +199,14 @@ def kernel_breakdown(torch, s, peaks):
     gemm_case("gemm_tcgen05 mlp2 x (gate+residual)", Mx, E, FH, 24, "gate")
 
     def attn_case(name, Tn, Tc, count, bounded=True):
-        qkv = normed_qkv(torch, B, Tn, dev)
+        qkv = normed_qkv(torch, B, Tn, dev, prescale=bounded)
         oc = torch.empty(B, max(Tc, 1), E, device=dev, dtype=torch.bfloat16)
         ox = torch.empty(B, Tn - Tc, E, device=dev, dtype=torch.bfloat16)
         # the step's launches: q and k are RMS-normed by the QKV epilogue (weights 1 in this random-init
-        # model), the engine passes the bound that follows from the norm weights
-        bound = QK_SCORE_BOUND if bounded else 0.0
+        # model), q pre-scaled; the engine passes scale 0 and the bound that follows from the norm weights
+        bound, scale = (QK_SCORE_BOUND * QK_PRESCALE, 0.0) if bounded else (0.0, 0.125)
         fn = lambda: s.check(s.lib().sd3_attention_bounded(s.ptr(qkv), B, Tn, NH, Tc, s.ptr(oc) if Tc else None,
-                                                           s.ptr(ox), 0.125, bound, None, 0, s.stream_ptr()))
+                                                           s.ptr(ox), scale, bound, None, 0, s.stream_ptr()))
         ms = time_events(torch, fn, 5)
         fl = 4.0 * B * NH * Tn * Tn * 64
         d = dict(kernel=name, launches_per_step=count, ms=round(ms, 4), achieved=round(fl / ms / 1e9, 1),
@@ -214,8 +214,8 @@ def kernel_breakdown(torch, s, peaks):
         out.append(d)
         return d
 
-    joint = attn_case("attention_tcgen05 joint T=4429 (bounded scores, as in the step)", T, TC, 24)
-    attn_case("attention_tcgen05 image-only T=4096 (bounded scores, as in the step)", TX, 0, 13)
+    joint = attn_case("attention_tcgen05 joint T=4429 (bounded scores, q pre-scaled: as in the step)", T, TC, 24)
+    attn_case("attention_tcgen05 image-only T=4096 (bounded scores, q pre-scaled: as in the step)", TX, 0, 13)
     attn_case("attention_tcgen05 joint T=4429, online softmax (no bound given)", T, TC, 0, bounded=False)
 
     x = torch.randn(Mx, E, device=dev)
@@ -305,7 +305,8 @@ def profile_case(name, reps=3):
         oc = torch.empty(Bp, max(Tc, 1), E, device=dev, dtype=torch.bfloat16)
         ox = torch.empty(Bp, Tn - Tc, E, device=dev, dtype=torch.bfloat16)
         fn = lambda: s.check(s.lib().sd3_attention_bounded(s.ptr(qkv), Bp, Tn, NH, Tc, s.ptr(oc) if Tc else None,
-                                                           s.ptr(ox), 0.125, QK_SCORE_BOUND, None, 0, s.stream_ptr()))
+                                                           s.ptr(ox), 0.0, QK_SCORE_BOUND * QK_PRESCALE, None, 0,
+                                                           s.stream_ptr()))
     elif name == "ln_mod":
         Bl = 8
         x = torch.randn(Bl * TX, E, device=dev)
@@ -443,11 +444,16 @@ def run_reference(args):
 QK_SCORE_BOUND = 1.01 * 64.0
 
 
-def normed_qkv(torch, batch, tokens, dev):
-    """Packed (batch, tokens, 3E) bf16 attention input as the QKV epilogue leaves it: q and k
-    RMS-normed per head (weights 1), v random."""
+QK_PRESCALE = 0.125 * 1.4426950408889634  # softmax scale * log2(e), folded into q by the engine
+
+
+def normed_qkv(torch, batch, tokens, dev, prescale=True):
+    """Packed (batch, tokens, 3E) bf16 attention input as the engine's QKV epilogue leaves it: q
+    and k RMS-normed per head (weights 1), q multiplied by softmax_scale * log2(e), v random."""
     raw = torch.randn(batch, tokens, 3, NH, 64, device=dev)
     raw[:, :, :2] *= torch.rsqrt(raw[:, :, :2].pow(2).mean(-1, keepdim=True) + 1e-6)
+    if prescale:
+        raw[:, :, 0] *= QK_PRESCALE
     return raw.reshape(batch, tokens, 3 * E).bfloat16()
 
 

@@ -201,11 +201,12 @@ __device__ __forceinline__ void exp_pack(uint32_t (&r)[32], float c, float nmc, 
 // by the magic-number add, f = s c - n in [-0.5, 0.5], the same degree-3 polynomial, exponent
 // added as an integer.  Needs |s c| < 2^22 and a finite result (the bounded mode guarantees
 // |s c| <= AT_BOUND_MAX); six packed FMAs and two integer operations per pair.
+template <bool UNIT>  // UNIT: c == 1, the scores are exp2 arguments already
 __device__ __forceinline__ float2 ex2_poly2(float2 s, float2 c2) {
   const float2 magic = make_float2(12582912.0f, 12582912.0f);
-  const float2 t = __ffma2_rn(s, c2, magic);
+  const float2 t = UNIT ? __fadd2_rn(s, magic) : __ffma2_rn(s, c2, magic);
   const float2 nn = __ffma2_rn(t, make_float2(-1.0f, -1.0f), magic);  // -round(s c)
-  const float2 f = __ffma2_rn(s, c2, nn);
+  const float2 f = UNIT ? __fadd2_rn(s, nn) : __ffma2_rn(s, c2, nn);
   float2 p = __ffma2_rn(f, make_float2(0.0558011f, 0.0558011f), make_float2(0.2402265f, 0.2402265f));
   p = __ffma2_rn(p, f, make_float2(0.6931472f, 0.6931472f));
   p = __ffma2_rn(p, f, make_float2(1.0f, 1.0f));
@@ -219,7 +220,7 @@ __device__ __forceinline__ float2 ex2_poly2(float2 s, float2 c2) {
 // FMA pipe (a microbenchmark of this loop: 7.2 clk per warp-wide element against 8.2 with every
 // exponential on the MUFU unit; 2/8 the same, 4/8 slower).  Without POLY a score of -inf (a
 // masked key) gives exactly 0.
-template <bool POLY>
+template <bool POLY, bool UNIT>
 __device__ __forceinline__ void exp2_pack(uint32_t (&r)[32], float c, float2& acc) {
   const float2 c2 = make_float2(c, c);
 #pragma unroll
@@ -227,9 +228,9 @@ __device__ __forceinline__ void exp2_pack(uint32_t (&r)[32], float c, float2& ac
     const float2 s = make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
     float2 p;
     if (POLY && ((AT_POLY_PAIRS >> (i % 8)) & 1)) {
-      p = ex2_poly2(s, c2);
+      p = ex2_poly2<UNIT>(s, c2);
     } else {
-      const float2 x = __fmul2_rn(s, c2);
+      const float2 x = UNIT ? s : __fmul2_rn(s, c2);
       p.x = ex2_approx(x.x);
       p.y = ex2_approx(x.y);
     }
@@ -243,7 +244,10 @@ __device__ __forceinline__ void exp2_pack(uint32_t (&r)[32], float c, float2& ac
 // nor vanish in fp32 / bf16 and the softmax needs no running maximum: no row maximum, no vote,
 // no rescaling of O; P = 2^(s c) and the row sum normalise the output exactly as before
 // (softmax is invariant to the subtracted constant).
-template <bool BOUNDED>
+// UNIT (bounded mode only): the queries were multiplied by scale log2(e) where they were formed
+// (the engine folds the factor into the RMSNorm weight of q), so a score is its own exp2
+// argument: one packed multiply per pair of scores less (measured: 4 % of the kernel).
+template <bool BOUNDED, bool UNIT>
 __global__ void __launch_bounds__(AT_THREADS, 2)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -408,8 +412,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
       tmem_wait_ld();
       if (ragged) { mask_cols(ra, kv0, T); mask_cols(rb, kv0 + 32, T); }
       if (BOUNDED) {
-        if (ragged) { exp2_pack<false>(ra, c, l2); exp2_pack<false>(rb, c, l2); }
-        else { exp2_pack<true>(ra, c, l2); exp2_pack<true>(rb, c, l2); }
+        if (ragged) { exp2_pack<false, UNIT>(ra, c, l2); exp2_pack<false, UNIT>(rb, c, l2); }
+        else { exp2_pack<true, UNIT>(ra, c, l2); exp2_pack<true, UNIT>(rb, c, l2); }
       } else {
         half_step(ra, rb, false);
       }
@@ -423,8 +427,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQKV, const AttnAr
       uint32_t pre_pv = 1;
       if (j >= 1) pre_pv = mbar_test_wait(&pv_done[stp], parp);
       if (BOUNDED) {
-        if (ragged) { exp2_pack<false>(rc, c, l2); exp2_pack<false>(rd, c, l2); }
-        else { exp2_pack<true>(rc, c, l2); exp2_pack<true>(rd, c, l2); }
+        if (ragged) { exp2_pack<false, UNIT>(rc, c, l2); exp2_pack<false, UNIT>(rd, c, l2); }
+        else { exp2_pack<true, UNIT>(rc, c, l2); exp2_pack<true, UNIT>(rd, c, l2); }
       } else {
         half_step(rc, rd, true);
       }
@@ -606,7 +610,9 @@ size_t attention_scratch_bytes(int B, int T, int NH) {
 
 // score_bound: an upper bound on |q . k| over every query and key of the launch, or 0 when none
 // is known.  With 0 < score_bound * scale * log2(e) <= 80 the softmax runs without a running
-// maximum (same result, about 8 % faster); any other value selects the online softmax.
+// maximum (same result, about 12 % faster); any other value selects the online softmax.
+// scale == 0: the queries already carry the factor scale * log2(e), the scores are used as exp2
+// arguments directly (and score_bound is a bound on those).
 int launch_attention_bf16(const bf16* qkv, int B, int T, int NH, int Tc, bf16* out_c, bf16* out_x,
                           float scale, int* dev_status, cudaStream_t stream, int out_e4m3, void* scratch,
                           size_t scratch_bytes, float score_bound) {
@@ -632,10 +638,13 @@ int launch_attention_bf16(const bf16* qkv, int B, int T, int NH, int Tc, bf16* o
   if (dev >= 0 && dev < 64) {
     std::lock_guard<std::mutex> lock(attr_mutex);
     if (!attr_done[dev]) {
-      cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<false>,
+      cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<false, false>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES);
       if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(attention_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(attention_tcgen05_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 AT_SMEM_BYTES);
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(attention_tcgen05_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  AT_SMEM_BYTES);
       if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(attention)");
       attr_done[dev] = true;
@@ -644,7 +653,8 @@ int launch_attention_bf16(const bf16* qkv, int B, int T, int NH, int Tc, bf16* o
   AttnArgs a;
   a.B = B; a.T = T; a.NH = NH; a.Tc = Tc; a.E = E;
   a.out_c = out_c; a.out_x = out_x;
-  a.scale_log2e = scale * 1.4426950408889634f;
+  const bool unit = scale == 0.0f;  // q carries scale log2(e) already
+  a.scale_log2e = unit ? 1.0f : scale * 1.4426950408889634f;
   a.out_e4m3 = out_e4m3;
   a.status = dev_status;
   const int qtiles = (T + AT_BM - 1) / AT_BM, nkv = (T + AT_BN - 1) / AT_BN;
@@ -662,10 +672,12 @@ int launch_attention_bf16(const bf16* qkv, int B, int T, int NH, int Tc, bf16* o
   }
   const dim3 grid(qtiles * a.kv_split, NH, B);
   const float bound_log2 = score_bound * fabsf(a.scale_log2e);
-  if (score_bound > 0.0f && bound_log2 <= AT_BOUND_MAX)
-    attention_tcgen05_kernel<true><<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(tm, a);
+  if (score_bound > 0.0f && bound_log2 <= AT_BOUND_MAX && unit)
+    attention_tcgen05_kernel<true, true><<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(tm, a);
+  else if (score_bound > 0.0f && bound_log2 <= AT_BOUND_MAX)
+    attention_tcgen05_kernel<true, false><<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(tm, a);
   else
-    attention_tcgen05_kernel<false><<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(tm, a);
+    attention_tcgen05_kernel<false, false><<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(tm, a);
   int lrc = after_launch("attention_tcgen05_kernel");
   if (lrc || a.kv_split == 1) return lrc;
   const long warps = static_cast<long>(B) * NH * T;

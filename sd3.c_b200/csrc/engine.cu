@@ -53,6 +53,10 @@ struct LayerW {
   // upper bounds on |q . k| of the joint and the image-only attention, from the RMSNorm weights of
   // q and k (0: none, the attention keeps its running maximum); set by sd3_model_finalize
   float joint_bound = 0.f, dual_bound = 0.f;
+  // Copies of the query RMSNorm weights multiplied by softmax_scale * log2(e) (set with the
+  // bounds): the QKV epilogue then leaves q pre-scaled, a score is its own exp2 argument and the
+  // attention kernel saves the multiply; joint_bound / dual_bound are in those units then.
+  float *c_wq_s = nullptr, *x_wq_s = nullptr, *d_wq_s = nullptr;
   long c_mod_off = 0, x_mod_off = 0;  // column offsets into the concatenated AdaLN output
   int c_chunks = 0, x_chunks = 0;
   bool dual = false, last = false;
@@ -375,8 +379,9 @@ int run_qkv(sd3_model* m, const Linear& L, const void* h, void* qkv, int B, int 
 
 // out_e4m3 (FP8 mode, head_dim 64 only): the outputs feed FP8 out-projections
 int run_attention(sd3_model* m, const void* qkv, int B, int T, int Tc, void* o_c, void* o_x,
-                  cudaStream_t st, bool out_e4m3 = false, float score_bound = 0.f) {
-  const float scale = 1.0f / sqrtf(static_cast<float>(m->D));
+                  cudaStream_t st, bool out_e4m3 = false, float score_bound = 0.f, bool prescaled = false) {
+  // prescaled: q already carries scale * log2(e) (only set up for the bf16 kernel)
+  const float scale = prescaled ? 0.0f : 1.0f / sqrtf(static_cast<float>(m->D));
   if (!m->f32 && m->D == 64)
     return launch_attention_bf16(static_cast<const bf16*>(qkv), B, T, m->NH, Tc,
                                  static_cast<bf16*>(o_c), static_cast<bf16*>(o_x), scale, m->status,
@@ -472,17 +477,21 @@ int block_body(sd3_model* m, int l, float* c, float* x, int B, int Tc, int Tx, c
   // QKV (context rows first, then image rows) and joint attention
   // the tensor-core path (bf16 / FP8 modes, head_dim 64): image and context GEMMs of a kind share a launch
   const bool grouped = !m->f32 && m->D == 64;
+  // q pre-scaled by softmax_scale * log2(e) through its norm weight (both streams or neither)
+  const bool pre_j = L.c_wq_s != nullptr && L.x_wq_s != nullptr;
+  const float* c_wq = pre_j ? L.c_wq_s : L.c_wq;
+  const float* x_wq = pre_j ? L.x_wq_s : L.x_wq;
   if (grouped) {
-    SD3_TRY(run_linear_pair(m, L.x_qkv, w.h_x, B * Tx, qkv_epilogue(m, w.qkv, Tx, T, Tc, L.x_wq, L.x_wk), x8a,
-                            L.c_qkv, w.h_c, B * Tc, qkv_epilogue(m, w.qkv, Tc, T, 0, L.c_wq, L.c_wk), c8a, st));
+    SD3_TRY(run_linear_pair(m, L.x_qkv, w.h_x, B * Tx, qkv_epilogue(m, w.qkv, Tx, T, Tc, x_wq, L.x_wk), x8a,
+                            L.c_qkv, w.h_c, B * Tc, qkv_epilogue(m, w.qkv, Tc, T, 0, c_wq, L.c_wk), c8a, st));
   } else {
-    SD3_TRY(run_qkv(m, L.c_qkv, w.h_c, w.qkv, B, Tc, T, 0, L.c_wq, L.c_wk, st, c8a));
-    SD3_TRY(run_qkv(m, L.x_qkv, w.h_x, w.qkv, B, Tx, T, Tc, L.x_wq, L.x_wk, st, x8a));
+    SD3_TRY(run_qkv(m, L.c_qkv, w.h_c, w.qkv, B, Tc, T, 0, c_wq, L.c_wk, st, c8a));
+    SD3_TRY(run_qkv(m, L.x_qkv, w.h_x, w.qkv, B, Tx, T, Tc, x_wq, L.x_wk, st, x8a));
   }
   // FP8 mode: both out-projections of the joint attention must take e4m3 for the
   // kernel to write it (one flag for both outputs)
   const bool o8 = m->fp8 && m->D == 64 && L.x_out.w8 && (L.last || L.c_out.w8);
-  SD3_TRY(run_attention(m, w.qkv, B, T, Tc, L.last ? nullptr : w.o_c, w.o_x, st, o8, L.joint_bound));
+  SD3_TRY(run_attention(m, w.qkv, B, T, Tc, L.last ? nullptr : w.o_c, w.o_x, st, o8, L.joint_bound, pre_j));
   if (grouped && !L.last) {
     SD3_TRY(run_linear_pair(m, L.x_out, w.o_x, B * Tx, gate_epilogue(L.x_out, Tx, x_gate_a, ms, x), o8,
                             L.c_out, w.o_c, B * Tc, gate_epilogue(L.c_out, Tc, c_gate_a, ms, c), o8, st));
@@ -491,9 +500,10 @@ int block_body(sd3_model* m, int l, float* c, float* x, int B, int Tc, int Tx, c
     SD3_TRY(run_gate_resid(m, L.x_out, w.o_x, B, Tx, x_gate_a, ms, x, st, o8));
   }
   if (L.dual) {
-    SD3_TRY(run_qkv(m, L.d_qkv, w.h_x2, w.qkv2, B, Tx, Tx, 0, L.d_wq, L.d_wk, st, x8a));
+    const bool pre_d = L.d_wq_s != nullptr;
+    SD3_TRY(run_qkv(m, L.d_qkv, w.h_x2, w.qkv2, B, Tx, Tx, 0, pre_d ? L.d_wq_s : L.d_wq, L.d_wk, st, x8a));
     const bool o8d = m->fp8 && m->D == 64 && L.d_out.w8;
-    SD3_TRY(run_attention(m, w.qkv2, B, Tx, 0, nullptr, w.o_x2, st, o8d, L.dual_bound));
+    SD3_TRY(run_attention(m, w.qkv2, B, Tx, 0, nullptr, w.o_x2, st, o8d, L.dual_bound, pre_d));
     SD3_TRY(run_gate_resid(m, L.d_out, w.o_x2, B, Tx, x_gate_2, ms, x, st, o8d));
   }
   // MLPs of both streams: LayerNorm + modulate each, then the two first linears (GELU-tanh) and
@@ -563,6 +573,9 @@ int quantize_block_weights(sd3_model* m) {
 // After the per-head RMSNorm (module_tests/modules.py:286-297: x / sqrt(mean(x^2) + eps) * w) a
 // head vector has norm at most sqrt(D) max|w|, whatever the input; so |q . k| <= D max|wq| max|wk|
 // for every query and key of an attention.  1 % on top covers the bf16 rounding of q and k.
+// Where the bound is small enough for the attention kernel's bounded softmax, the query norm
+// weights also get a copy multiplied by softmax_scale * log2(e): q leaves the QKV epilogue
+// pre-scaled (one rounding to bf16, as before) and the bound is stored in those units.
 int compute_score_bounds(sd3_model* m) {
   for (LayerW& L : m->layers) L.joint_bound = L.dual_bound = 0.f;
   if (!m->cfg.use_qk_norm || m->f32 || m->D != 64) return ST_OK;
@@ -579,14 +592,39 @@ int compute_score_bounds(sd3_model* m) {
     for (float v : h) a = std::max(a, std::fabs(v));
     return std::isfinite(a) ? a : (ok = false, 0.f);
   };
+  // the bounded softmax takes exp2 arguments of at most 80: a looser bound would not be used,
+  // and then q stays unscaled and the attention keeps its running maximum
+  const float c = 1.4426950408889634f / sqrtf(static_cast<float>(m->D));
+  auto scaled_copy = [&](const float* w, float** dst) -> int {
+    if (cudaMemcpy(h.data(), w, sizeof(float) * m->D, cudaMemcpyDeviceToHost) != cudaSuccess)
+      return check_cuda(cudaGetLastError(), "read norm weight");
+    for (float& v : h) v *= c;
+    if (!*dst) {
+      int r = dev_alloc(m, reinterpret_cast<void**>(dst), sizeof(float) * m->D);
+      if (r) return r;
+    }
+    return check_cuda(cudaMemcpy(*dst, h.data(), sizeof(float) * m->D, cudaMemcpyHostToDevice), "write norm weight");
+  };
   for (LayerW& L : m->layers) {
     ok = true;
     const float q = std::max(amax(L.c_wq), amax(L.x_wq)), k = std::max(amax(L.c_wk), amax(L.x_wk));
-    if (ok) L.joint_bound = 1.01f * m->D * q * k;
+    const float jb = 1.01f * m->D * q * k * c;
+    if (ok && jb > 0.f && jb <= 80.0f) {
+      if ((rc = scaled_copy(L.c_wq, &L.c_wq_s)) || (rc = scaled_copy(L.x_wq, &L.x_wq_s))) return rc;
+      L.joint_bound = jb;
+    } else {
+      L.c_wq_s = L.x_wq_s = nullptr;  // (a buffer from an earlier finalize stays owned by the model)
+    }
     if (L.dual) {
       ok = true;
       const float q2 = amax(L.d_wq), k2 = amax(L.d_wk);
-      if (ok) L.dual_bound = 1.01f * m->D * q2 * k2;
+      const float db = 1.01f * m->D * q2 * k2 * c;
+      if (ok && db > 0.f && db <= 80.0f) {
+        if ((rc = scaled_copy(L.d_wq, &L.d_wq_s))) return rc;
+        L.dual_bound = db;
+      } else {
+        L.d_wq_s = nullptr;
+      }
     }
   }
   return ST_OK;

@@ -151,18 +151,29 @@ class PackedModel:
         self.ada_w = torch.cat(ws, 0).contiguous()
         self.ada_b = torch.cat(bs, 0).contiguous()
         self.ada_total = off
-        # bounds on |q . k| of each block's joint and image-only attention, from the q/k RMSNorm
-        # weights (0.0: no norm, the attention keeps its running maximum)
+        # Bounds on the scores of each block's joint and image-only attention, from the q/k RMSNorm
+        # weights.  Where a bound is small enough for the kernel's bounded softmax (exp2 arguments
+        # of at most 80), the query norm weights are replaced by copies that carry
+        # softmax_scale * log2(e): q leaves the QKV epilogue pre-scaled, the attention is called
+        # with scale 0 and the bound in those units.  Otherwise (0.0, plain scale) nothing changes.
         self.score_bound = {}
+        c = 1.4426950408889634 * (cfg["emb_dim"] // cfg["attn_heads"]) ** -0.5
         for l in range(L):
             pre = "transformer.%d." % l
-            def norms(kind, streams):
-                return [self.w[pre + s_ + "_rmsnorm_" + kind + ".weight"] for s_ in streams
+            def names(kind, streams):
+                return [pre + s_ + "_rmsnorm_" + kind + ".weight" for s_ in streams
                         if pre + s_ + "_rmsnorm_" + kind + ".weight" in self.w]
-            q, k = norms("query", ("context", "latent")), norms("key", ("context", "latent"))
-            joint = sd3.qk_norm_score_bound(q, k) if len(q) == 2 and len(k) == 2 else 0.0
-            q2, k2 = norms("query", ("latent_dual",)), norms("key", ("latent_dual",))
-            dual = sd3.qk_norm_score_bound(q2, k2) if q2 and k2 else 0.0
+            def bound(qn, kn, want):
+                if len(qn) != want or len(kn) != want:
+                    return 0.0
+                b = sd3.qk_norm_score_bound([self.w[n] for n in qn], [self.w[n] for n in kn]) * c
+                if not 0.0 < b <= 80.0:
+                    return 0.0
+                for n in qn:
+                    self.w[n] = (self.w[n] * c).contiguous()
+                return b
+            joint = bound(names("query", ("context", "latent")), names("key", ("context", "latent")), 2)
+            dual = bound(names("query", ("latent_dual",)), names("key", ("latent_dual",)), 1)
             self.score_bound[l] = (joint, dual)
         self.local = None
         self.ws = {}
@@ -295,8 +306,9 @@ def block_forward(pm, l, mod, c, x_loc, comm, last, dual):
     wq, wk = rms("latent")
     sd3.qkv_project_groups(B["h_x"], w, b, wq, wk, 1e-6, B["send"], E, P)
     comm.all_to_all_into(att_in[0, Tc:], B["send"])
-    _attention_into(sd3, att_in, Tc + Tx, NH // P, Tc, scale, None if last else B["o_c"], B["o_x"], B["attn_scratch"],
-                    pm.score_bound[l][0])
+    jb, db = pm.score_bound[l]
+    _attention_into(sd3, att_in, Tc + Tx, NH // P, Tc, 0.0 if jb > 0.0 else scale, None if last else B["o_c"], B["o_x"],
+                    B["attn_scratch"], jb)
     comm.all_to_all_into(B["recv_o"], B["o_x"])
     B["o_rows"].view(Tl, P, Eh).copy_(B["recv_o"].permute(1, 0, 2))
     if not last:
@@ -312,7 +324,7 @@ def block_forward(pm, l, mod, c, x_loc, comm, last, dual):
         wq, wk = rms("latent_dual")
         sd3.qkv_project_groups(B["h_x2"], w, b, wq, wk, 1e-6, B["send"], E, P)
         comm.all_to_all_into(B["att2"][0], B["send"])
-        _attention_into(sd3, B["att2"], Tx, NH // P, 0, scale, None, B["o_x"], B["attn_scratch"], pm.score_bound[l][1])
+        _attention_into(sd3, B["att2"], Tx, NH // P, 0, 0.0 if db > 0.0 else scale, None, B["o_x"], B["attn_scratch"], db)
         comm.all_to_all_into(B["recv_o"], B["o_x"])
         B["o_rows"].view(Tl, P, Eh).copy_(B["recv_o"].permute(1, 0, 2))
         w, b = pm.lin(pre + "latent_dual_attn_Wout")

@@ -390,3 +390,28 @@ def test_attention_bound_above_limit_uses_online_softmax(sd3):
     assert torch.isfinite(ox.float()).all()
     assert rel_l2(ox, ref) < 2e-2
     assert sd3.device_status() == 0
+
+
+@pytest.mark.parametrize("B,T,NH,Tc", [(2, 1357, 3, 333), (1, 4429, 2, 333), (2, 130, 2, 0)])
+def test_attention_prescaled_queries(sd3, B, T, NH, Tc):
+    """scale == 0: the queries carry softmax_scale * log2(e) already (the engine folds the factor
+    into the RMSNorm weight of q), the scores are exp2 arguments; bounded and online softmax."""
+    c = 0.125 * 1.4426950408889634
+    wq = torch.full((64,), 1.2, device="cuda")
+    wk = torch.full((64,), 0.8, device="cuda")
+    qkv = _normed_qkv(B, T, NH, wq, wk, seed=T + 2)
+    E = NH * 64
+    pre = qkv.clone()
+    pre[..., :E] = (qkv[..., :E].float() * c).bfloat16()
+    bound = sd3.qk_norm_score_bound(wq, wk) * c
+    oc0, ox0 = sd3.attention(qkv, B, T, NH, Tc, 0.125)
+    oc1, ox1 = sd3.attention(pre, B, T, NH, Tc, 0.0, score_bound=bound)  # bounded, unit scale
+    oc2, ox2 = sd3.attention(pre, B, T, NH, Tc, 0.0)                     # online softmax, unit scale
+    torch.cuda.synchronize()
+    assert sd3.device_status() == 0
+    q, k, v = [t.view(B, T, NH, 64).transpose(1, 2).float() for t in qkv.chunk(3, -1)]
+    ref = torch.nn.functional.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, T, E)
+    for oc, ox in ((oc1, ox1), (oc2, ox2)):
+        got = torch.cat([oc, ox], 1) if oc is not None else ox
+        assert rel_l2(got, ref) < 1e-2
+        assert rel_l2(ox, ox0) < 8e-3
