@@ -50,9 +50,9 @@ B, TC, HW, TX = 8, 333, 128, 4096
 E, NH, FH = 1536, 24, 6144
 T = TC + TX
 # DRAM bytes (read + written) of one joint-attention launch per sample, from the ncu
-# capture of `--profile-case attn_joint` (batch 2: 81.70 MB read + 9.88 MB written);
+# capture of `--profile-case attn_joint` (batch 2: 81.74 MB read + 7.83 MB written);
 # it is the compulsory q|k|v read and O write, so it grows in proportion to the batch.
-ATTN_TRAFFIC_BYTES_PER_SAMPLE = int((81.70e6 + 9.88e6) / 2)
+ATTN_TRAFFIC_BYTES_PER_SAMPLE = int((81.74e6 + 7.83e6) / 2)
 
 
 def load_binding():
