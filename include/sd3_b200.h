@@ -146,13 +146,16 @@ SD3_API int sd3_attention_ws(const void* qkv_bf16, int B, int T, int num_heads, 
 
 /* sd3_attention_ws for callers that know an upper bound on |q . k| over every query and key of
  * the call (score_bound, in raw dot-product units; 0 = unknown).  After the q/k RMSNorm of the
- * model (module_tests/modules.py:286-297) every head vector has norm at most
- * sqrt(head_dim) * max|weight|, so score_bound = 64 * max|wq| * max|wk| (times 1.01 for the
- * bf16 rounding of q and k) holds for any input.  If score_bound * scale * log2(e) <= 80, the
+ * model (module_tests/modules.py:286-297) every head vector is x_hat * weight with
+ * |x_hat|^2 <= head_dim, so score_bound = 64 * max_d |wq_d * wk_d| (times 1.01 for the bf16
+ * rounding of q and k) holds for any input.  If score_bound * scale * log2(e) <= 80, the
  * softmax is evaluated as 2^(s c) / sum 2^(s c) without a running maximum -- identical in exact
  * arithmetic, no overflow or underflow possible within the bound, fewer instructions per score;
  * otherwise, and for score_bound <= 0, this is sd3_attention_ws.  A bound that does not hold
- * gives undefined results (inf / NaN), never a device fault.  scratch may be null. */
+ * gives undefined results (inf / NaN), never a device fault.  scratch may be null.
+ * scale == 0: the queries already carry scale * log2(e) (a score is its own exp2 argument);
+ * score_bound is then a bound on those scores.  Accepted by sd3_attention and
+ * sd3_attention_ws too. */
 SD3_API int sd3_attention_bounded(const void* qkv_bf16, int B, int T, int num_heads, int Tc, void* out_c_bf16,
                                   void* out_x_bf16, float scale, float score_bound, void* scratch,
                                   long scratch_bytes, void* stream);

@@ -571,8 +571,10 @@ int quantize_block_weights(sd3_model* m) {
 }
 
 // After the per-head RMSNorm (module_tests/modules.py:286-297: x / sqrt(mean(x^2) + eps) * w) a
-// head vector has norm at most sqrt(D) max|w|, whatever the input; so |q . k| <= D max|wq| max|wk|
-// for every query and key of an attention.  1 % on top covers the bf16 rounding of q and k.
+// head vector is x_hat * w with |x_hat|^2 <= D, whatever the input; so |q . k| = |sum_d x_d y_d wq_d wk_d|
+// <= D max_d |wq_d wk_d| for every query and key of an attention (context and image streams share
+// the joint attention: element-wise maxima of their weights).  1 % on top covers the bf16 rounding
+// of q and k.
 // Where the bound is small enough for the attention kernel's bounded softmax, the query norm
 // weights also get a copy multiplied by softmax_scale * log2(e): q leaves the QKV epilogue
 // pre-scaled (one rounding to bf16, as before) and the bound is stored in those units.
@@ -583,14 +585,23 @@ int compute_score_bounds(sd3_model* m) {
   if (rc) return rc;
   std::vector<float> h(m->D);
   bool ok = true;
-  auto amax = [&](const float* w) {
+  // |w| of a norm weight, element-wise maximum over the streams that share an attention
+  auto absmax_into = [&](const float* w, std::vector<float>& acc) {
     if (!w || cudaMemcpy(h.data(), w, sizeof(float) * m->D, cudaMemcpyDeviceToHost) != cudaSuccess) {
       ok = false;
-      return 0.f;
+      return;
     }
+    for (int d = 0; d < m->D; ++d) {
+      if (!std::isfinite(h[d])) ok = false;
+      acc[d] = std::max(acc[d], std::fabs(h[d]));
+    }
+  };
+  // sum_d x_d y_d a_d with |x|^2 = |y|^2 = D is at most D max_d a_d: the bound needs the largest
+  // PRODUCT |wq_d wk_d|, not the product of the largest weights
+  auto pair_bound = [&](const std::vector<float>& q, const std::vector<float>& k) {
     float a = 0.f;
-    for (float v : h) a = std::max(a, std::fabs(v));
-    return std::isfinite(a) ? a : (ok = false, 0.f);
+    for (int d = 0; d < m->D; ++d) a = std::max(a, q[d] * k[d]);
+    return a;
   };
   // the bounded softmax takes exp2 arguments of at most 80: a looser bound would not be used,
   // and then q stays unscaled and the attention keeps its running maximum
@@ -607,8 +618,10 @@ int compute_score_bounds(sd3_model* m) {
   };
   for (LayerW& L : m->layers) {
     ok = true;
-    const float q = std::max(amax(L.c_wq), amax(L.x_wq)), k = std::max(amax(L.c_wk), amax(L.x_wk));
-    const float jb = 1.01f * m->D * q * k * c;
+    std::vector<float> q(m->D, 0.f), k(m->D, 0.f);
+    absmax_into(L.c_wq, q); absmax_into(L.x_wq, q);
+    absmax_into(L.c_wk, k); absmax_into(L.x_wk, k);
+    const float jb = 1.01f * m->D * pair_bound(q, k) * c;
     if (ok && jb > 0.f && jb <= 80.0f) {
       if ((rc = scaled_copy(L.c_wq, &L.c_wq_s)) || (rc = scaled_copy(L.x_wq, &L.x_wq_s))) return rc;
       L.joint_bound = jb;
@@ -617,8 +630,10 @@ int compute_score_bounds(sd3_model* m) {
     }
     if (L.dual) {
       ok = true;
-      const float q2 = amax(L.d_wq), k2 = amax(L.d_wk);
-      const float db = 1.01f * m->D * q2 * k2 * c;
+      std::vector<float> q2(m->D, 0.f), k2(m->D, 0.f);
+      absmax_into(L.d_wq, q2);
+      absmax_into(L.d_wk, k2);
+      const float db = 1.01f * m->D * pair_bound(q2, k2) * c;
       if (ok && db > 0.f && db <= 80.0f) {
         if ((rc = scaled_copy(L.d_wq, &L.d_wq_s))) return rc;
         L.dual_bound = db;

@@ -225,12 +225,14 @@ def qkv_project_groups(x_bf16, w_nk_bf16, bias, wq, wk, eps, out, E_out, head_gr
 
 def qk_norm_score_bound(wq, wk, head_dim=64):
     """Upper bound on |q . k| after the per-head RMSNorm with weights wq, wk (tensors, or lists of
-    tensors when several norms feed one attention): every normed head vector has norm at most
-    sqrt(head_dim) * max|w|; 1 % on top for the bf16 rounding of q and k."""
-    def amax(w):
+    tensors when several norms feed one attention): a normed head vector is x_hat * w with
+    |x_hat|^2 <= head_dim, so |q . k| <= head_dim * max_d |wq_d wk_d| (element-wise maxima over
+    the listed weights); 1 % on top for the bf16 rounding of q and k."""
+    torch = _torch()
+    def absmax(w):
         ws = w if isinstance(w, (list, tuple)) else [w]
-        return max(float(t.detach().abs().max()) for t in ws)
-    return 1.01 * head_dim * amax(wq) * amax(wk)
+        return torch.stack([t.detach().float().abs().reshape(-1) for t in ws]).amax(0)
+    return 1.01 * head_dim * float((absmax(wq) * absmax(wk)).max())
 
 
 def attention(qkv_bf16, B, T, num_heads, Tc, scale, want_context=True, scratch=None, score_bound=0.0):

@@ -336,3 +336,62 @@ def test_full_model_2048px_long_sequence_bf16(sd3):
     """One 2048x2048 image: latent 16x256x256 -> 16384 image tokens + 333 context tokens
     through the whole denoiser on one GPU."""
     _full_model_case(sd3, 1, 256, seed=4)
+
+
+def _toy_with_norm_gain(gain):
+    """The golden toy model (head_dim 64) with every q/k RMSNorm weight multiplied by `gain`,
+    and its output from the fp32 oracle on the CPU."""
+    g = golden("model_toy.pt")
+    cfg = g["config"]
+    p = {k: (v.float() * gain).bfloat16() if "rmsnorm" in k else v.bfloat16() for k, v in g["params"].items()}
+    args = [g["pooled"].bfloat16(), g["captions"].bfloat16(), g["latent"].bfloat16(), g["timesteps"]]
+    with torch.no_grad():
+        ref = O.dit_forward(args[0].float(), args[1].float(), args[2].float(), args[3],
+                            {k: v.float() for k, v in p.items()}, cfg["num_layers"], cfg["dual_attention_layers"],
+                            cfg["attn_heads"], cfg["patch_size"], cfg["pos_embed_max_size"], cfg["base_height"], True)
+    return cfg, p, args, ref
+
+
+@pytest.mark.parametrize("gain", [0.5, 1.0, 2.0, 3.0, 6.0])
+def test_model_qk_norm_gain_selects_softmax_mode(sd3, gain):
+    """The engine derives a bound on |q . k| from the q/k RMSNorm weights: small weights run the
+    bounded softmax with pre-scaled queries (gain <= 2 here: 64 * max|wq wk| * 0.18 <= 80), large
+    ones keep the online softmax.  Either way the output matches the fp32 oracle."""
+    cfg, p, args, ref = _toy_with_norm_gain(gain)
+    m = make_model(sd3, cfg, p, sd3.PRECISION_BF16)
+    out = m.forward(*[a.cuda() for a in args])
+    torch.cuda.synchronize()
+    assert sd3.device_status() == 0
+    m.close()
+    assert torch.isfinite(out.float()).all()
+    assert rel_l2(out, ref) < 1.5e-2
+
+
+def test_model_norm_weights_rewritten_after_finalize(sd3):
+    """Rewriting the norm weights after finalize moves a model between the two softmax modes;
+    after the next finalize it gives the bits of a model built with those weights."""
+    cfg, p_small, args, _ = _toy_with_norm_gain(1.0)
+    _, p_large, _, _ = _toy_with_norm_gain(6.0)
+    dev_args = [a.cuda() for a in args]
+    outs = {}
+    for name, p in (("small", p_small), ("large", p_large)):
+        m = make_model(sd3, cfg, p, sd3.PRECISION_BF16)
+        outs[name] = m.forward(*dev_args).clone()
+        m.close()
+    m = make_model(sd3, cfg, p_small, sd3.PRECISION_BF16)
+    for k, v in p_large.items():
+        if "rmsnorm" in k:
+            m.set_param(k, v.cuda())
+    m.load({})  # finalize again
+    out_l = m.forward(*dev_args).clone()
+    for k, v in p_small.items():
+        if "rmsnorm" in k:
+            m.set_param(k, v.cuda())
+    m.load({})
+    out_s = m.forward(*dev_args).clone()
+    torch.cuda.synchronize()
+    assert sd3.device_status() == 0
+    m.close()
+    assert torch.equal(out_l, outs["large"])
+    assert torch.equal(out_s, outs["small"])
+    assert not torch.equal(outs["small"], outs["large"])
