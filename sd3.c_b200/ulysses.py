@@ -88,6 +88,18 @@ class DistComm:
     def all_gather_into(self, out, t):
         self.dist.all_gather_into_tensor(out.reshape(-1), t.reshape(-1), group=self.group)
 
+    def all_to_all_start(self, out, send):
+        """all_to_all_into that returns at once with a handle: the exchange runs on the
+        communicator's stream behind the work already queued on the current stream, and the
+        current stream only waits for it at handle.wait().  Neither buffer may be touched
+        between the two calls."""
+        return self.dist.all_to_all_single(out.reshape(-1), send.reshape(-1), group=self.group, async_op=True)
+
+
+class _Done:
+    def wait(self):
+        return True
+
 
 class LocalComm:
     """The one-rank communicator: every exchange is a copy.  Lets the sharded forward run
@@ -106,6 +118,10 @@ class LocalComm:
 
     def all_gather_into(self, out, t):
         out.reshape(-1).copy_(t.reshape(-1))
+
+    def all_to_all_start(self, out, send):
+        out.reshape(-1).copy_(send.reshape(-1))
+        return _Done()
 
 
 # ---------------------------------------------------------------------------
@@ -211,6 +227,7 @@ class PackedModel:
         e = lambda *shape: torch.empty(shape, device=dev, dtype=bf)
         b = dict(h_c=e(Tc, E), h_x=e(Tl, E), h_x2=e(Tl, E), send=e(P, Tl, 3, Eh), att_in=e(1, Tc + P * Tl, 3 * Eh),
                  att2=e(1, P * Tl, 3 * Eh), o_c=e(1, Tc, Eh), o_x=e(1, P * Tl, Eh), recv_o=e(P, Tl, Eh),
+                 send2=e(P, Tl, 3, Eh), o_x2=e(1, P * Tl, Eh), recv_o2=e(P, Tl, Eh),  # dual attention's own set
                  o_rows=e(Tl, E), gath_c=e(P, Tc, Eh), o_ctx=e(Tc, E), hid_x=e(Tl, F), hid_c=e(Tc, F),
                  mod=torch.empty((1, self.ada_total), device=dev, dtype=torch.float32))
         NHl = self.cfg["attn_heads"] // P
@@ -299,17 +316,35 @@ def block_forward(pm, l, mod, c, x_loc, comm, last, dual):
 
     # joint attention: context rows (my heads) | image rows of every rank (my heads)
     att_in = B["att_in"]
-    wl, bl = ctx_local[l]
-    wq, wk = rms("context")
-    sd3.qkv_project_groups(B["h_c"], wl, bl, wq, wk, 1e-6, att_in, Eh, 1)  # rows [0, Tc) of att_in
     w, b = pm.lin(pre + "latent_to_qkv")
     wq, wk = rms("latent")
     sd3.qkv_project_groups(B["h_x"], w, b, wq, wk, 1e-6, B["send"], E, P)
-    comm.all_to_all_into(att_in[0, Tc:], B["send"])
     jb, db = pm.score_bound[l]
+    # The exchanges of a dual block are pipelined: each all-to-all runs on the communicator's
+    # stream under the next kernel of the other attention (the image-only QKV under the first
+    # exchange, the joint attention under the second, the image-only attention under the third,
+    # the joint out-projection under the fourth).  A plain block has nothing to put under its
+    # two exchanges but the small context projection.
+    h_in = comm.all_to_all_start(att_in[0, Tc:], B["send"])
+    h_in2 = None
+    if dual:
+        w, b = pm.lin(pre + "latent_dual_to_qkv")
+        wq, wk = rms("latent_dual")
+        sd3.qkv_project_groups(B["h_x2"], w, b, wq, wk, 1e-6, B["send2"], E, P)
+        h_in2 = comm.all_to_all_start(B["att2"][0], B["send2"])
+    wl, bl = ctx_local[l]
+    wq, wk = rms("context")
+    sd3.qkv_project_groups(B["h_c"], wl, bl, wq, wk, 1e-6, att_in, Eh, 1)  # rows [0, Tc) of att_in
+    h_in.wait()
     _attention_into(sd3, att_in, Tc + Tx, NH // P, Tc, 0.0 if jb > 0.0 else scale, None if last else B["o_c"], B["o_x"],
                     B["attn_scratch"], jb)
-    comm.all_to_all_into(B["recv_o"], B["o_x"])
+    h_out = comm.all_to_all_start(B["recv_o"], B["o_x"])
+    h_out2 = None
+    if dual:  # image-only attention of the dual blocks
+        h_in2.wait()
+        _attention_into(sd3, B["att2"], Tx, NH // P, 0, 0.0 if db > 0.0 else scale, None, B["o_x2"], B["attn_scratch"], db)
+        h_out2 = comm.all_to_all_start(B["recv_o2"], B["o_x2"])
+    h_out.wait()
     B["o_rows"].view(Tl, P, Eh).copy_(B["recv_o"].permute(1, 0, 2))
     if not last:
         comm.all_gather_into(B["gath_c"], B["o_c"])
@@ -318,15 +353,9 @@ def block_forward(pm, l, mod, c, x_loc, comm, last, dual):
         _gate_resid(sd3, B["o_ctx"], w, b, c_gate_a, c)
     w, b = pm.lin(pre + "latent_attn_Wout")
     _gate_resid(sd3, B["o_rows"], w, b, x_gate_a, x_loc)
-
-    if dual:  # image-only attention of the dual blocks
-        w, b = pm.lin(pre + "latent_dual_to_qkv")
-        wq, wk = rms("latent_dual")
-        sd3.qkv_project_groups(B["h_x2"], w, b, wq, wk, 1e-6, B["send"], E, P)
-        comm.all_to_all_into(B["att2"][0], B["send"])
-        _attention_into(sd3, B["att2"], Tx, NH // P, 0, 0.0 if db > 0.0 else scale, None, B["o_x"], B["attn_scratch"], db)
-        comm.all_to_all_into(B["recv_o"], B["o_x"])
-        B["o_rows"].view(Tl, P, Eh).copy_(B["recv_o"].permute(1, 0, 2))
+    if dual:
+        h_out2.wait()
+        B["o_rows"].view(Tl, P, Eh).copy_(B["recv_o2"].permute(1, 0, 2))
         w, b = pm.lin(pre + "latent_dual_attn_Wout")
         _gate_resid(sd3, B["o_rows"], w, b, ch(xm, 8), x_loc)
 
