@@ -1,6 +1,6 @@
 // CTA-pair variant of the tcgen05 GEMM: two CTAs (a cluster of two on
-// neighbouring SMs) cooperate on 256 x 256 (or, for problems with too few of
-// those to fill the machine, 256 x 128) output tiles with
+// neighbouring SMs) cooperate on 256 x 256 (or, for problems of less than half a
+// wave of those, 256 x 128) output tiles with
 // tcgen05.mma.cta_group::2.  One launch can carry TWO problems of the same
 // shape class (same N, K and epilogue: the image-stream GEMM of a block and its
 // small context-stream twin); the persistent tile loop runs the first problem's
@@ -346,14 +346,17 @@ int build_problem(PairProblem* pp, const GemmProblem& q, int operand_dtype, int 
   return ST_OK;
 }
 
-// 256-wide tiles unless they would leave much of the last wave empty and 128-wide ones would not
-// (the narrow tile moves a third more operand bytes per FLOP, so it has to win clearly).
+// 256-wide tiles, except for problems so small that even twice as many 128-wide tiles fit in one
+// wave of CTA pairs.  The narrow tile moves a third more operand bytes per FLOP (96 instead of
+// 64 bytes per clock per SM at the full MMA rate), and with every SM busy the L2 cannot supply
+// that: measured at 4096-4429 rows (1.3-1.5 waves of wide tiles, where wave arithmetic favours
+// the narrow ones) the wide tiles are 15-25 % faster (N = 1536, K = 6144: 72 against 90 us), at
+// 2048 rows 35 %.  Only when few SMs are active (at most 1536 rows at N = 1536) do the narrow
+// tiles win, by 5-8 %.
 int choose_tile_width(long tiles256, const GemmEpilogue& epi) {
   if (!narrow_tiles_built(epi)) return 256;
   const long pairs = device_sm_count() / 2;
-  if (pairs <= 0 || tiles256 >= 6 * pairs) return 256;
-  auto fill = [&](long tiles) { return static_cast<double>(tiles) / static_cast<double>(((tiles + pairs - 1) / pairs) * pairs); };
-  return 0.92 * fill(2 * tiles256) > fill(tiles256) + 0.03 ? 128 : 256;
+  return (pairs > 0 && 2 * tiles256 <= pairs) ? 128 : 256;
 }
 
 }  // namespace
