@@ -390,6 +390,7 @@ class Model:
               "sd3_model_create")
 
     def close(self):
+        self._graphs = {}
         if self.handle:
             lib().sd3_model_destroy(self.handle)
             self.handle = c_void_p()
@@ -401,6 +402,7 @@ class Model:
             pass
 
     def set_param(self, name, tensor):
+        self._graphs = {}  # captured forwards refer to the parameters as they were
         shape = (c_int64 * tensor.dim())(*tensor.shape)
         check(lib().sd3_model_set_param(self.handle, name.encode(), ptr(tensor), dtype_tag(tensor),
                                         tensor.dim(), shape, stream_ptr()),
@@ -414,6 +416,7 @@ class Model:
         return self
 
     def reserve(self, B, Tc, H, W):
+        self._graphs = {}  # the workspace may move
         check(lib().sd3_model_reserve(self.handle, B, Tc, H, W), "sd3_model_reserve")
 
     def forward(self, pooled, captions, latent, timesteps, out=None):
@@ -427,6 +430,40 @@ class Model:
                                     ptr(out), dtype_tag(latent), B, Tc, H, W, stream_ptr()),
               "sd3_dit_forward")
         return out
+
+    def forward_graphed(self, pooled, captions, latent, timesteps, out):
+        """forward() on exactly these tensors, replayed as one CUDA graph: the first call for a
+        set of tensor addresses and shapes runs the forward once eagerly (which reserves the
+        workspace), captures it on the current stream and replays it; later calls only replay.
+        For loops that call the denoiser on fixed device buffers (a sampler's latent buffer, a
+        serving slot): at one sample per GPU the ~270 launches of a step otherwise cost about
+        2 % of it.  The tensors must stay alive and in place; a larger problem, set_param and
+        reserve drop the captured graphs.  Returns `out`."""
+        torch = _torch()
+        args = (pooled, captions, latent, timesteps, out)
+        key = tuple((t.data_ptr(), tuple(t.shape), str(t.dtype)) for t in args)
+        graphs = self.__dict__.setdefault("_graphs", {})
+        entry = graphs.get(key)
+        if entry is None:
+            if len(graphs) >= 8:
+                graphs.clear()
+            self.forward(pooled, captions, latent, timesteps, out)
+            torch.cuda.synchronize()
+            n0 = lib().sd3_launch_count(0)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.forward(pooled, captions, latent, timesteps, out)
+            launches = int(lib().sd3_launch_count(0) - n0)
+            entry = graphs[key] = (g, launches, args)
+        entry[0].replay()
+        return out
+
+    def graph_launches(self, pooled, captions, latent, timesteps, out):
+        """Kernel launches inside the graph forward_graphed replays for these tensors (0 if none
+        has been captured)."""
+        key = tuple((t.data_ptr(), tuple(t.shape), str(t.dtype)) for t in (pooled, captions, latent, timesteps, out))
+        entry = self.__dict__.get("_graphs", {}).get(key)
+        return entry[1] if entry else 0
 
     def block_forward(self, layer, y, c, x):
         B, Tc, E = c.shape

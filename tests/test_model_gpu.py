@@ -395,3 +395,26 @@ def test_model_norm_weights_rewritten_after_finalize(sd3):
     assert torch.equal(out_l, outs["large"])
     assert torch.equal(out_s, outs["small"])
     assert not torch.equal(outs["small"], outs["large"])
+
+
+def test_forward_graphed_matches_eager(sd3):
+    """Model.forward_graphed replays the forward as one CUDA graph: same bits as the eager call,
+    new inputs written into the same tensors are picked up, and the launch count is recorded."""
+    g = golden("model_toy.pt")
+    m = make_model(sd3, g["config"], g["params"], sd3.PRECISION_BF16)
+    args = [g["pooled"].bfloat16().cuda(), g["captions"].bfloat16().cuda(), g["latent"].bfloat16().cuda(),
+            g["timesteps"].float().cuda()]
+    eager = m.forward(*args).clone()
+    out = torch.empty_like(eager)
+    m.forward_graphed(*args, out)
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager)
+    assert m.graph_launches(*args, out) > 20
+    # the graph reads the tensors it was captured on: change their contents, replay
+    args[2].mul_(0.5)
+    eager2 = m.forward(*args).clone()
+    m.forward_graphed(*args, out)
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager2) and not torch.equal(eager2, eager)
+    assert sd3.device_status() == 0
+    m.close()
