@@ -36,6 +36,15 @@
 //    was 6 % slower), every eighth exponential is evaluated as a polynomial on
 //    the FMA pipe, and the multiply-subtract / row-sum pairs use the packed
 //    f32x2 instructions.
+//  * Three instantiations.  <false, false>: the online softmax above, for any input.
+//    <true, *>: the caller gives a bound on |q . k| (SD3.5 normalises q and k per head, so
+//    64 max_d |wq_d wk_d| bounds every score whatever the input); when the exp2 argument can
+//    not exceed 80 in magnitude, P = 2^(s c) needs no running maximum at all -- no row
+//    maximum, vote, branch or rescale -- and three of every eight PAIRS of exponentials go to
+//    the FMA pipe as packed polynomials.  <true, true>: the queries were also multiplied by
+//    scale log2(e) where they were formed, so a score is its own exp2 argument.  The kernel's
+//    time follows its instruction count (no pipe is saturated; two warps per sub-partition
+//    are bound by their own dependent-issue latency): -17 % warp instructions, -14 % time.
 //
 // Replaces mha_cuda (cuda/dit.cu:612-652: two cublasSgemmStridedBatched calls
 // around scale_softmax_kernel2, cuda/dit.cu:548-608, over materialised T x T
