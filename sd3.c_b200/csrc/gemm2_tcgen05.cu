@@ -349,9 +349,9 @@ int build_problem(PairProblem* pp, const GemmProblem& q, int operand_dtype, int 
 // 256-wide tiles, except for problems so small that even twice as many 128-wide tiles fit in one
 // wave of CTA pairs.  Shared memory moves 128 bytes per clock; at the full MMA rate the wide tile
 // asks for 64 (TMA fill) + 96 (tensor-core reads) = 160, the narrow one for 96 + 128 = 224, so
-// their ceilings are 0.80 and 0.57 of the MMA rate: measured at 4096-4429 rows (1.3-1.5 waves of wide tiles, where wave arithmetic favours the
-// narrow ones) the wide tiles are 15-25 % faster (N = 1536, K = 6144: 72 against 90 us), at
-// 2048 rows 35 %.  Only for problems of a few tiles (at most 1536 rows at N = 1536), where the
+// their ceilings are 0.80 and 0.57 of the MMA rate.  Measured at 4096-4429 rows (1.3-1.5 waves of
+// wide tiles, where wave arithmetic favours the narrow ones) the wide tiles are 15-25 % faster
+// (N = 1536, K = 6144: 72 against 90 us), at 2048 rows 35 %.  Only for problems of a few tiles (at most 1536 rows at N = 1536), where the
 // narrow tiles put twice as many SMs to work, do they win, by 5-8 %.
 int choose_tile_width(long tiles256, const GemmEpilogue& epi) {
   if (!narrow_tiles_built(epi)) return 256;
