@@ -307,7 +307,12 @@ SD3_API int sd3_model_set_param(sd3_model* m, const char* name, const void* dev_
                         const int64_t* shape, void* stream);
 
 /* Checks that every parameter the configuration needs was provided.  Writes
- * the number of missing parameters to *missing (details via sd3_last_error). */
+ * the number of missing parameters to *missing (details via sd3_last_error).
+ * Synchronises the device: it waits for the parameter copies, derives from the
+ * q/k RMSNorm weights the bound on the attention scores of every block (which
+ * selects the softmax mode of sd3_attention_bounded inside the forward) and,
+ * in FP8 mode, quantises the block weights.  Call it again after a later
+ * sd3_model_set_param. */
 SD3_API int sd3_model_finalize(sd3_model* m, int* missing);
 
 /* Allocates (or grows) the activation workspace for the given problem size.
