@@ -695,7 +695,8 @@ def main():
         # HostPipeline.submit uploads the batch on a copy stream, runs the denoiser, downloads
         # the result; with two device input sets the copies of neighbouring steps overlap the
         # compute.  All of it is inside the timed region (the last download is waited for).
-        pipe = s.HostPipeline(model, nb, TC, 16, HW, HW, 2048, 4096, torch.bfloat16, depth=2)
+        pipe = s.HostPipeline(model, nb, TC, 16, HW, HW, 2048, 4096, torch.bfloat16, depth=2,
+                              use_graph=not args.no_graph)
 
     def e2e_run():
         if pipe is not None:
@@ -803,7 +804,7 @@ def main():
                 "call": "sd3_b200.HostPipeline.submit (pinned host batch -> sd3_dit_forward -> pinned host)"},
         "e2e_extension": ext,
         "gpu_launches": int(launches),
-        "launch_mode": "kernel by kernel" if args.no_graph else "value: one CUDA graph replay per step; e2e: kernel by kernel",
+        "launch_mode": "kernel by kernel" if args.no_graph else "one CUDA graph replay per step (value and e2e); e2e_extension kernel by kernel",
         "clocks": clocks,
         "step_tflops_per_gpu": round(step_tf, 1),
         "step_frac_of_sustained_peak": round(step_tf / peaks["bf16_tflops_sustained"], 4),

@@ -482,9 +482,12 @@ class HostPipeline:
     one, so the upload of batch i+1 and the download of batch i-1 overlap the
     compute of batch i; the order of work on a set is kept by events.  Nothing
     is allocated after construction.  `flush()` makes the current stream wait
-    for the last download (call it before reading the host buffers or timing)."""
+    for the last download (call it before reading the host buffers or timing).
+    With use_graph (the default) the forward on each device input set is captured
+    once as a CUDA graph and replayed (Model.forward_graphed): the sets are fixed
+    device buffers, which is what that needs."""
 
-    def __init__(self, model, B, Tc, C, H, W, pooled_dim, captions_dim, dtype=None, depth=2):
+    def __init__(self, model, B, Tc, C, H, W, pooled_dim, captions_dim, dtype=None, depth=2, use_graph=True):
         torch = _torch()
         dtype = dtype or torch.bfloat16
         self.model = model
@@ -501,6 +504,7 @@ class HostPipeline:
                 uploaded=torch.cuda.Event(), computed=torch.cuda.Event(), drained=torch.cuda.Event()))
         self.count = 0
         self.last = None
+        self.use_graph = use_graph
         model.reserve(B, Tc, H, W)
 
     def submit(self, h_pooled, h_captions, h_latent, h_timesteps, h_out):
@@ -517,7 +521,8 @@ class HostPipeline:
             st["uploaded"].record(self.h2d)
         cur.wait_event(st["uploaded"])
         cur.wait_event(st["drained"])  # the download that last read this set's output is over
-        self.model.forward(st["pooled"], st["captions"], st["latent"], st["t"], st["out"])
+        fwd = self.model.forward_graphed if self.use_graph else self.model.forward
+        fwd(st["pooled"], st["captions"], st["latent"], st["t"], st["out"])
         st["computed"].record(cur)
         with torch.cuda.stream(self.d2h):
             self.d2h.wait_event(st["computed"])

@@ -8,8 +8,8 @@ from conftest import golden
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("depth", [1, 2, 3])
-def test_pipelined_batches_equal_direct_forward(sd3, depth):
+@pytest.mark.parametrize("depth,use_graph", [(1, True), (2, True), (3, True), (2, False)])
+def test_pipelined_batches_equal_direct_forward(sd3, depth, use_graph):
     g = golden("model_toy.pt")
     cfg = g["config"]
     m = sd3.Model(cfg["num_layers"], cfg["dual_attention_layers"], cfg["pooled_dim"], cfg["captions_dim"],
@@ -28,7 +28,7 @@ def test_pipelined_batches_equal_direct_forward(sd3, depth):
             t=(torch.rand(B, generator=gen) * 1000).pin_memory(),
             out=torch.zeros(g["latent"].shape, dtype=torch.bfloat16).pin_memory()))
     pipe = sd3.HostPipeline(m, B, Tc, C, H, W, g["pooled"].shape[1], g["captions"].shape[2], torch.bfloat16,
-                            depth=depth)
+                            depth=depth, use_graph=use_graph)
     for b in batches:
         pipe.submit(b["pooled"], b["captions"], b["latent"], b["t"], b["out"])
     pipe.flush()
