@@ -451,7 +451,9 @@ class Model:
             torch.cuda.synchronize()
             n0 = lib().sd3_launch_count(0)
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            # thread-local capture mode: other host threads (a communicator's watchdog, a data
+            # loader) may keep calling the CUDA runtime while this thread captures
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
                 self.forward(pooled, captions, latent, timesteps, out)
             launches = int(lib().sd3_launch_count(0) - n0)
             entry = graphs[key] = (g, launches, args)
