@@ -101,6 +101,22 @@ SD3_API int sd3_linear_gate_residual(const void* x_bf16, const void* w_nk_bf16, 
                              const float* gate, long gate_stride, int rows_per_sample,
                              float* resid, int M, int N, int K, void* stream);
 
+/* Two sd3_linear / sd3_linear_gate_residual calls of the same N, K, activation and output
+ * type as ONE launch: the tiles of the second problem run in the tail of the first's, so a
+ * small GEMM (the 333-row context stream next to the image stream of the same block:
+ * context_mlp / latent_mlp, context_attn_Wout / latent_attn_Wout, cuda/dit.cu:825-903) costs
+ * no launch and no part-filled wave of its own.  Falls back to two launches where the
+ * CTA-pair kernel does not cover both shapes.  Each problem has its own operands, weights,
+ * bias (gate, residual) and row count. */
+SD3_API int sd3_linear_pair(const void* x0_bf16, const void* w0_nk_bf16, const float* bias0, void* out0, int M0,
+                            const void* x1_bf16, const void* w1_nk_bf16, const float* bias1, void* out1, int M1,
+                            int out_dtype, int N, int K, int act, void* stream);
+SD3_API int sd3_linear_gate_residual_pair(const void* x0_bf16, const void* w0_nk_bf16, const float* bias0,
+                                          const float* gate0, int rows_per_sample0, float* resid0, int M0,
+                                          const void* x1_bf16, const void* w1_nk_bf16, const float* bias1,
+                                          const float* gate1, int rows_per_sample1, float* resid1, int M1,
+                                          long gate_stride, int N, int K, void* stream);
+
 /* QKV projection with fused per-head RMSNorm of q and k (head_dim 64) and the
  * token concatenation: row m = (b, t) of x goes to row b*T_total + row_offset
  * + t of qkv_out (B, T_total, 3E) bf16.  wq/wk are the (64,) RMSNorm weights

@@ -149,6 +149,64 @@ int sd3_linear_gate_residual(const void* x, const void* w, const float* bias, co
   return launch_gemm(x, K, w, K, OPERAND_BF16, M, N, K, e, device_status_word(), S(stream));
 }
 
+int sd3_linear_pair(const void* x0, const void* w0, const float* bias0, void* out0, int M0, const void* x1,
+                    const void* w1, const float* bias1, void* out1, int M1, int out_dtype, int N, int K, int act,
+                    void* stream) {
+  if (!dtype_ok(out_dtype) || (act != SD3_ACT_NONE && act != SD3_ACT_GELU_TANH) || M0 <= 0 || M1 <= 0) {
+    set_last_error("sd3_linear_pair: bad out_dtype %d, act %d or row counts %d, %d", out_dtype, act, M0, M1);
+    return SD3_ERR_INVALID_ARG;
+  }
+  GemmProblem p[2];
+  const void* xs[2] = {x0, x1};
+  const void* ws[2] = {w0, w1};
+  const float* bs[2] = {bias0, bias1};
+  void* outs[2] = {out0, out1};
+  const int Ms[2] = {M0, M1};
+  for (int i = 0; i < 2; ++i) {
+    p[i].A = xs[i]; p[i].lda = K; p[i].W = ws[i]; p[i].ldw = K; p[i].M = Ms[i];
+    p[i].epi.mode = act == SD3_ACT_GELU_TANH ? EPI_BIAS_GELU : EPI_BIAS;
+    p[i].epi.bias = bs[i];
+    p[i].epi.out = outs[i];
+    p[i].epi.out_f32 = out_dtype == SD3_DTYPE_F32;
+    p[i].epi.ldo = N;
+  }
+  return launch_gemm_grouped(p[0], p[1], OPERAND_BF16, N, K, device_status_word(), S(stream));
+}
+
+int sd3_linear_gate_residual_pair(const void* x0, const void* w0, const float* bias0, const float* gate0,
+                                  int rows_per_sample0, float* resid0, int M0, const void* x1, const void* w1,
+                                  const float* bias1, const float* gate1, int rows_per_sample1, float* resid1,
+                                  int M1, long gate_stride, int N, int K, void* stream) {
+  if (rows_per_sample0 <= 0 || rows_per_sample1 <= 0 || M0 <= 0 || M1 <= 0) {
+    set_last_error("sd3_linear_gate_residual_pair: row counts must be positive");
+    return SD3_ERR_INVALID_ARG;
+  }
+  GemmProblem p[2];
+  const void* xs[2] = {x0, x1};
+  const void* ws[2] = {w0, w1};
+  const float* bs[2] = {bias0, bias1};
+  const float* gs[2] = {gate0, gate1};
+  float* rs[2] = {resid0, resid1};
+  const int Ms[2] = {M0, M1};
+  const int rps[2] = {rows_per_sample0, rows_per_sample1};
+  for (int i = 0; i < 2; ++i) {
+    p[i].A = xs[i]; p[i].lda = K; p[i].W = ws[i]; p[i].ldw = K; p[i].M = Ms[i];
+    GemmEpilogue& e = p[i].epi;
+    e.mode = EPI_GATE_RESID;
+    e.bias = bs[i];
+    e.out = rs[i];
+    e.resid = rs[i];
+    e.out_f32 = 1;
+    e.ldo = N;
+    e.gate = gs[i];
+    e.gate_stride = gate_stride;
+    e.rows_in = rps[i];
+    e.rows_out = rps[i];
+    e.row_off = 0;
+  }
+  return launch_gemm_grouped(p[0], p[1], OPERAND_BF16, N, K, device_status_word(), S(stream));
+}
+
 int sd3_qkv_project(const void* x, const void* w, const float* bias, const float* wq,
                     const float* wk, float eps, void* qkv_out, int B, int T_in, int T_total,
                     int row_offset, int E, void* stream) {

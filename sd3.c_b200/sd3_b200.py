@@ -62,6 +62,8 @@ PROTOTYPES = {
     "sd3_quantize_e4m3": (c_int, [c_void_p, c_int, c_void_p, c_long, c_float, c_void_p]),
     "sd3_linear_gate_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
     "sd3_qkv_project": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "sd3_linear_pair": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "sd3_linear_gate_residual_pair": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_long, c_int, c_int, c_void_p]),
     "sd3_qkv_project_groups": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "sd3_attention": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p]),
     "sd3_attention_scratch_bytes": (c_long, [c_int, c_int, c_int]),

@@ -245,6 +245,35 @@ def _gate_resid(sd3, x_bf16, w, b, gate_row, resid):
         x_bf16.shape[0], w.shape[0], x_bf16.shape[1], sd3.stream_ptr()), "sd3_linear_gate_residual")
 
 
+# The context rows' GEMMs ride in the launches of the image rows' GEMMs of the same kind
+# (sd3_linear_pair, sd3_linear_gate_residual_pair); False launches them separately.
+PAIR_LAUNCHES = True
+
+
+def _gate_resid_pair(sd3, x0, w0, b0, gate0, resid0, x1, w1, b1, gate1, resid1):
+    """Two gate+residual GEMMs of one shape class (image rows and context rows of a block) as
+    one launch; one sample each, so one gate row each."""
+    if not PAIR_LAUNCHES:
+        _gate_resid(sd3, x0, w0, b0, gate0, resid0)
+        _gate_resid(sd3, x1, w1, b1, gate1, resid1)
+        return
+    sd3.check(sd3.lib().sd3_linear_gate_residual_pair(
+        sd3.ptr(x0), sd3.ptr(w0), sd3.ptr(b0), gate0.data_ptr(), resid0.shape[0], sd3.ptr(resid0), x0.shape[0],
+        sd3.ptr(x1), sd3.ptr(w1), sd3.ptr(b1), gate1.data_ptr(), resid1.shape[0], sd3.ptr(resid1), x1.shape[0],
+        0, w0.shape[0], x0.shape[1], sd3.stream_ptr()), "sd3_linear_gate_residual_pair")
+
+
+def _linear_pair_into(sd3, x0, w0, b0, out0, x1, w1, b1, out1, act=0):
+    if not PAIR_LAUNCHES:
+        _linear_into(sd3, x0, w0, b0, out0, act=act)
+        _linear_into(sd3, x1, w1, b1, out1, act=act)
+        return
+    sd3.check(sd3.lib().sd3_linear_pair(sd3.ptr(x0), sd3.ptr(w0), sd3.ptr(b0), sd3.ptr(out0), x0.shape[0],
+                                        sd3.ptr(x1), sd3.ptr(w1), sd3.ptr(b1), sd3.ptr(out1), x1.shape[0],
+                                        sd3.dtype_tag(out0), w0.shape[0], x0.shape[1], act, sd3.stream_ptr()),
+              "sd3_linear_pair")
+
+
 def _ln_mod(sd3, x, E, eps, shift, scale, out1, shift2=None, scale2=None, out2=None):
     """LayerNorm + modulate of (rows, E) f32 rows of one sample into preallocated bf16 outputs."""
     from ctypes import c_void_p
@@ -346,13 +375,15 @@ def block_forward(pm, l, mod, c, x_loc, comm, last, dual):
         h_out2 = comm.all_to_all_start(B["recv_o2"], B["o_x2"])
     h_out.wait()
     B["o_rows"].view(Tl, P, Eh).copy_(B["recv_o"].permute(1, 0, 2))
+    w, b = pm.lin(pre + "latent_attn_Wout")
     if not last:
         comm.all_gather_into(B["gath_c"], B["o_c"])
         B["o_ctx"].view(Tc, P, Eh).copy_(B["gath_c"].permute(1, 0, 2))
-        w, b = pm.lin(pre + "context_attn_Wout")
-        _gate_resid(sd3, B["o_ctx"], w, b, c_gate_a, c)
-    w, b = pm.lin(pre + "latent_attn_Wout")
-    _gate_resid(sd3, B["o_rows"], w, b, x_gate_a, x_loc)
+        wc_, bc_ = pm.lin(pre + "context_attn_Wout")
+        # the replicated context rows ride in the tail of the image rows' launch
+        _gate_resid_pair(sd3, B["o_rows"], w, b, x_gate_a, x_loc, B["o_ctx"], wc_, bc_, c_gate_a, c)
+    else:
+        _gate_resid(sd3, B["o_rows"], w, b, x_gate_a, x_loc)
     if dual:
         h_out2.wait()
         B["o_rows"].view(Tl, P, Eh).copy_(B["recv_o2"].permute(1, 0, 2))
@@ -360,16 +391,17 @@ def block_forward(pm, l, mod, c, x_loc, comm, last, dual):
         _gate_resid(sd3, B["o_rows"], w, b, ch(xm, 8), x_loc)
 
     _ln_mod(sd3, x_loc, E, 1e-6, x_shift_m, x_scale_m, B["h_x"])
-    w, b = pm.lin(pre + "latent_mlp.lin1")
-    _linear_into(sd3, B["h_x"], w, b, B["hid_x"], act=sd3.ACT_GELU_TANH)
-    w, b = pm.lin(pre + "latent_mlp.lin2")
-    _gate_resid(sd3, B["hid_x"], w, b, x_gate_m, x_loc)
-    if not last:
+    w1, b1 = pm.lin(pre + "latent_mlp.lin1")
+    w2, b2 = pm.lin(pre + "latent_mlp.lin2")
+    if not last:  # both streams' MLPs: each linear of the pair as one launch
         _ln_mod(sd3, c, E, 1e-6, c_shift_m, c_scale_m, B["h_c"])
-        w, b = pm.lin(pre + "context_mlp.lin1")
-        _linear_into(sd3, B["h_c"], w, b, B["hid_c"], act=sd3.ACT_GELU_TANH)
-        w, b = pm.lin(pre + "context_mlp.lin2")
-        _gate_resid(sd3, B["hid_c"], w, b, c_gate_m, c)
+        wc1, bc1 = pm.lin(pre + "context_mlp.lin1")
+        wc2, bc2 = pm.lin(pre + "context_mlp.lin2")
+        _linear_pair_into(sd3, B["h_x"], w1, b1, B["hid_x"], B["h_c"], wc1, bc1, B["hid_c"], act=sd3.ACT_GELU_TANH)
+        _gate_resid_pair(sd3, B["hid_x"], w2, b2, x_gate_m, x_loc, B["hid_c"], wc2, bc2, c_gate_m, c)
+    else:
+        _linear_into(sd3, B["h_x"], w1, b1, B["hid_x"], act=sd3.ACT_GELU_TANH)
+        _gate_resid(sd3, B["hid_x"], w2, b2, x_gate_m, x_loc)
 
 
 def dit_forward_sharded(pm, pooled, captions, latent, timesteps, comm):

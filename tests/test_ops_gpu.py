@@ -415,3 +415,36 @@ def test_attention_prescaled_queries(sd3, B, T, NH, Tc):
         got = torch.cat([oc, ox], 1) if oc is not None else ox
         assert rel_l2(got, ref) < 1e-2
         assert rel_l2(ox, ox0) < 8e-3
+
+
+@pytest.mark.parametrize("M0,M1,N,K,act", [(4096, 333, 1536, 1536, 0), (2048, 333, 6144, 1536, 1), (512, 77, 256, 256, 0),
+                                           (300, 300, 1536, 6144, 0)])
+def test_linear_pair_equals_two_linears(sd3, M0, M1, N, K, act):
+    """sd3_linear_pair / sd3_linear_gate_residual_pair: two GEMMs of one shape class in one
+    launch give what the two single calls give."""
+    from ctypes import c_void_p
+    gen = torch.Generator(device="cuda").manual_seed(M0 + M1 + N)
+    xs = [torch.randn(m, K, device="cuda", generator=gen).bfloat16() for m in (M0, M1)]
+    ws = [(torch.randn(N, K, device="cuda", generator=gen) * 0.03).bfloat16() for _ in range(2)]
+    bs = [torch.randn(N, device="cuda", generator=gen) * 0.1 for _ in range(2)]
+    ref = [sd3.linear(xs[i], ws[i], bs[i], act=act) for i in range(2)]
+    outs = [torch.empty_like(r) for r in ref]
+    sd3.check(sd3.lib().sd3_linear_pair(sd3.ptr(xs[0]), sd3.ptr(ws[0]), sd3.ptr(bs[0]), sd3.ptr(outs[0]), M0,
+                                        sd3.ptr(xs[1]), sd3.ptr(ws[1]), sd3.ptr(bs[1]), sd3.ptr(outs[1]), M1,
+                                        sd3.dtype_tag(outs[0]), N, K, act, sd3.stream_ptr()), "sd3_linear_pair")
+    torch.cuda.synchronize()
+    for o, r in zip(outs, ref):
+        assert rel_l2(o, r) < 1e-5
+    # gate + residual form
+    gates = [torch.randn(1, N, device="cuda", generator=gen) for _ in range(2)]
+    res0 = [torch.randn(m, N, device="cuda", generator=gen) for m in (M0, M1)]
+    want = [sd3.linear_gate_residual(xs[i], ws[i], bs[i], gates[i], xs[i].shape[0], res0[i].clone()) for i in range(2)]
+    got = [r.clone() for r in res0]
+    sd3.check(sd3.lib().sd3_linear_gate_residual_pair(
+        sd3.ptr(xs[0]), sd3.ptr(ws[0]), sd3.ptr(bs[0]), sd3.ptr(gates[0]), M0, sd3.ptr(got[0]), M0,
+        sd3.ptr(xs[1]), sd3.ptr(ws[1]), sd3.ptr(bs[1]), sd3.ptr(gates[1]), M1, sd3.ptr(got[1]), M1,
+        0, N, K, sd3.stream_ptr()), "sd3_linear_gate_residual_pair")
+    torch.cuda.synchronize()
+    assert sd3.device_status() == 0
+    for o, r in zip(got, want):
+        assert rel_l2(o, r) < 1e-5
