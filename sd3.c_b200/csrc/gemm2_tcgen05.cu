@@ -347,11 +347,12 @@ int build_problem(PairProblem* pp, const GemmProblem& q, int operand_dtype, int 
 }
 
 // 256-wide tiles, except for problems so small that even twice as many 128-wide tiles fit in one
-// wave of CTA pairs.  Shared memory moves 128 bytes per clock; at the full MMA rate the wide tile
-// asks for 64 (TMA fill) + 96 (tensor-core reads) = 160, the narrow one for 96 + 128 = 224, so
-// their ceilings are 0.80 and 0.57 of the MMA rate.  Measured at 4096-4429 rows (1.3-1.5 waves of
-// wide tiles, where wave arithmetic favours the narrow ones) the wide tiles are 15-25 % faster
-// (N = 1536, K = 6144: 72 against 90 us), at 2048 rows 35 %.  Only for problems of a few tiles (at most 1536 rows at N = 1536), where the
+// wave of CTA pairs.  The narrow tile needs 96 bytes of operands per clock per SM at the full MMA
+// rate against 64, and its ring slots (48 KiB) are consumed in half the time of the wide tile's
+// (64 KiB) while their refill takes as long: it reaches 0.5-0.6 of the MMA rate where the wide
+// tile reaches 0.8.  Measured at 4096-4429 rows (1.3-1.5 waves of wide tiles, where wave
+// arithmetic favours the narrow ones) the wide tiles are 15-25 % faster (N = 1536, K = 6144: 72
+// against 90 us), at 2048 rows 35 %.  Only for problems of a few tiles (at most 1536 rows at N = 1536), where the
 // narrow tiles put twice as many SMs to work, do they win, by 5-8 %.
 int choose_tile_width(long tiles256, const GemmEpilogue& epi) {
   if (!narrow_tiles_built(epi)) return 256;
