@@ -14,7 +14,12 @@
 // for a 128 x 256 tile); the tensor cores of both SMs read the two W halves
 // from both shared memories.  That cuts the L2 -> shared-memory traffic per
 // FLOP by a third and leaves room for a six-stage ring.  The even CTA of the
-// pair issues all MMAs; completion is signalled to both CTAs with
+// pair issues all MMAs, from TWO threads that take the ring's slots in turn: a
+// tcgen05.mma holds its issuing thread for about as long as it runs, so with one
+// thread the barrier test, the commit and the descriptor arithmetic of every slot
+// were idle time of the tensor pipe; now they run under the other thread's MMAs
+// (a turn counter in shared memory, bracketed by tcgen05 fences, keeps the MMAs
+// in K order).  Completion is signalled to both CTAs with
 // tcgen05.commit ... multicast::cluster.  Each CTA keeps the accumulator rows
 // of its own half of M in its own TMEM (two buffers of 256 columns) and drains
 // them through the same fused epilogues as the one-CTA kernel.
@@ -57,7 +62,8 @@ __host__ __device__ constexpr int pair_stages(int pbn) { return pbn == 256 ? 6 :
 __host__ __device__ constexpr int pair_red_bytes(int epi, bool out_f32) {
   return pair_stages_out(epi, out_f32) ? EPI_WARPS * P_RED_BYTES : 0;
 }
-constexpr int P_THREADS = 64 + 32 * EPI_WARPS;
+constexpr int P_THREADS = 64 + 32 * EPI_WARPS + 32;  // + a second MMA-issuing warp
+constexpr int P_MMA2_WARP = 2 + EPI_WARPS;
 __host__ __device__ constexpr int pair_smem_bytes(int epi, bool out_f32, int pbn) {
   return pair_stages(pbn) * pair_stage_bytes(pbn) + pair_red_bytes(epi, out_f32) + 256 + 1024;
 }
@@ -90,6 +96,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ PairProblem p0, const __grid_co
   uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   int* s_abort = reinterpret_cast<int*>(tmem_slot + 1);
+  volatile uint32_t* s_issued = reinterpret_cast<volatile uint32_t*>(s_abort + 1);  // slots whose MMAs have been issued
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -107,6 +114,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ PairProblem p0, const __grid_co
       mbar_init(&tempty_bar[a], 2 * EPI_WARPS);  // epilogue warps of both CTAs (leader's copy is used)
     }
     *s_abort = 0;
+    *s_issued = 0;
     fence_barrier_init();
     prefetch_tmap(&p0.tmA);
     prefetch_tmap(&p0.tmW);
@@ -159,56 +167,70 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ PairProblem p0, const __grid_co
         if (++stage == NSLOT) { stage = 0; phase ^= 1; }
       }
     }
-  } else if (warp == 1 && lane == 0) {
-    // ------------------------------ MMA issuer (leader only) ------------------
+  } else if ((warp == 1 || warp == P_MMA2_WARP) && lane == 0) {
+    // ------------------------------ MMA issuers (leader only) -----------------
+    // Two threads take the slots in turn: while one issues the eight MMAs of its slot the
+    // other waits for the operands of the next one, and the commit and the barrier work of a
+    // slot run under the other thread's MMAs.  `s_issued` hands the turn over, so the MMAs
+    // reach the tensor pipe in K order.
     if (rank == 0) {
+      const uint32_t me = warp == 1 ? 0u : 1u;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
+      uint32_t slot_no = 0;
       bool ok = true;
-      bool stage_ready = false;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, wc, DEV_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
-        tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * PBN);
         for (int ks = 0; ks < KS; ++ks) {
-          // The readiness of this slot was tested while the previous slot's
-          // MMAs were being issued; only fall back to a blocking wait if that
-          // early test failed.
-          if (!stage_ready) {
+          if ((slot_no & 1u) == me) {
+            if (ks == 0 && !mbar_wait(&tempty_bar[acc], acc_phase ^ 1, wc, DEV_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
             if (!mbar_wait(&full_bar[stage], phase, wc, DEV_TIMEOUT_FULL)) { ok = false; break; }
-          }
-          int ns = stage + 1;
-          uint32_t np = phase;
-          if (ns == NSLOT) { ns = 0; np ^= 1; }
-          const uint32_t next_ready = mbar_test_wait(&full_bar[ns], np);  // result consumed after the MMAs
-          tc_fence_after_sync();
-          const int nk = KB - 2 * ks < 2 ? KB - 2 * ks : 2;
-          for (int hs = 0; hs < nk; ++hs) {
-            const uint32_t a_addr = smem_u32(smem + (2 * stage + hs) * P_STAGE_BYTES);
-            const uint64_t a_desc = make_smem_desc_sw128(a_addr, 16, 1024);
-            const uint64_t b_desc = make_smem_desc_sw128(a_addr + P_A_BYTES, 16, 1024);
-#pragma unroll
-            for (int k = 0; k < P_KBYTES / 32; ++k) {
-              const uint64_t adv = static_cast<uint64_t>((k * 32) >> 4);
-              if constexpr (FP8)
-                mma_f8_ss_pair(d_tmem, a_desc + adv, b_desc + adv, IDESC, (ks | hs | k) != 0);
-              else
-                mma_f16_ss_pair(d_tmem, a_desc + adv, b_desc + adv, IDESC, (ks | hs | k) != 0);
+            {  // my turn: every earlier slot has been issued
+              const uint64_t t0 = global_timer_ns();
+              uint32_t it = 0;
+              while (*s_issued != slot_no) {
+                if (((++it) & 0x3ffu) == 0) {
+                  if (*wc.s_abort) { ok = false; break; }
+                  if (global_timer_ns() - t0 > SD3_WAIT_LIMIT_NS) {
+                    *wc.s_abort = 1;
+                    if (wc.g_status) atomicCAS(wc.g_status, 0, DEV_TIMEOUT_FULL);
+                    ok = false;
+                    break;
+                  }
+                }
+              }
+              if (!ok) break;
             }
+            tc_fence_after_sync();
+            const int nk = KB - 2 * ks < 2 ? KB - 2 * ks : 2;
+            for (int hs = 0; hs < nk; ++hs) {
+              const uint32_t a_addr = smem_u32(smem + (2 * stage + hs) * P_STAGE_BYTES);
+              const uint64_t a_desc = make_smem_desc_sw128(a_addr, 16, 1024);
+              const uint64_t b_desc = make_smem_desc_sw128(a_addr + P_A_BYTES, 16, 1024);
+#pragma unroll
+              for (int k = 0; k < P_KBYTES / 32; ++k) {
+                const uint64_t adv = static_cast<uint64_t>((k * 32) >> 4);
+                if constexpr (FP8)
+                  mma_f8_ss_pair(d_tmem, a_desc + adv, b_desc + adv, IDESC, (ks | hs | k) != 0);
+                else
+                  mma_f16_ss_pair(d_tmem, a_desc + adv, b_desc + adv, IDESC, (ks | hs | k) != 0);
+              }
+            }
+            tc_fence_before_sync();
+            *s_issued = slot_no + 1;  // the other thread may issue the next slot
+            mma_commit_pair(&empty_bar[stage], 3);          // frees the slot in both CTAs
+            if (ks == KS - 1) mma_commit_pair(&tfull_bar[acc], 3);  // accumulator ready in both CTAs
           }
-          mma_commit_pair(&empty_bar[stage], 3);          // frees the slot in both CTAs
-          if (ks == KS - 1) mma_commit_pair(&tfull_bar[acc], 3);  // accumulator ready in both CTAs
-          stage = ns;
-          phase = np;
-          stage_ready = next_ready != 0;
+          ++slot_no;
+          if (++stage == NSLOT) { stage = 0; phase ^= 1; }
         }
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
     }
-  } else if (warp >= 2) {
+  } else if (warp >= 2 && warp < 2 + EPI_WARPS) {
     // ------------------------------ epilogue (both CTAs) ----------------------
     const int quad = warp & 3;
     const int half = (warp - 2) >> 2;
