@@ -143,3 +143,60 @@ def test_qkv_project_head_group_layout(rows, E, K, G):
     torch.cuda.synchronize()
     assert sd3.device_status() == 0
     assert ((out.float() - ref).norm() / ref.norm()).item() < 1e-2
+
+
+def _gloo_worker(rank, world, port, ret):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        U = load_ulysses()
+        comm = U.DistComm()
+        torch.manual_seed(7)  # same tensors on every rank
+        NH, D, Tc, Tl = 4, 8, 3, 5
+        E, P = NH * D, world
+        Eh = E // P
+        ctx = torch.randn(Tc, 3 * E)
+        img = torch.randn(P * Tl, 3 * E)
+        mine = img[rank * Tl:(rank + 1) * Tl].contiguous()
+        send = U.split_heads_for_send(mine, P)                     # (P, Tl, 3, Eh)
+        recv = torch.empty_like(send)
+        h = comm.all_to_all_start(recv, send)                       # asynchronous form
+        recv2 = torch.empty_like(send)
+        comm.all_to_all_into(recv2, send)                           # blocking form
+        h.wait()
+        assert torch.equal(recv, recv2)
+        att_in = U.assemble_attention_input(ctx, recv, rank, P)     # (1, T, 3 Eh)
+        q, k, v = (t.reshape(1, Tc + P * Tl, NH // P, D) for t in att_in.chunk(3, -1))
+        o = O.attention(q, k, v)[0]                                 # my heads, all rows
+        back = torch.empty(P, Tl, Eh)
+        comm.all_to_all_into(back, U.split_tokens_for_send(o[Tc:].contiguous(), P))
+        rows = U.assemble_rows(back)                                # my rows, all heads
+        gath = torch.empty(P, Tc, Eh)
+        comm.all_gather_into(gath, o[:Tc].contiguous())
+        ret[rank] = (rows, U.assemble_rows(gath))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_exchanges_through_dist_comm_two_gloo_ranks():
+    """The communicator's three calls (blocking and asynchronous all-to-all, all-gather) on two
+    gloo ranks on the CPU: sharded attention equals the unsharded one."""
+    import torch.multiprocessing as mp
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 29700 + (os.getpid() % 1000)
+    mp.spawn(_gloo_worker, args=(2, port, ret), nprocs=2, join=True)
+    torch.manual_seed(7)
+    NH, D, Tc, Tl, P = 4, 8, 3, 5, 2
+    E = NH * D
+    ctx = torch.randn(Tc, 3 * E)
+    img = torch.randn(P * Tl, 3 * E)
+    full = torch.cat([ctx, img], 0)
+    q, k, v = (t.reshape(1, Tc + P * Tl, NH, D) for t in full.chunk(3, -1))
+    ref = O.attention(q, k, v)[0]
+    for r in range(P):
+        rows, ctx_rows = ret[r]
+        assert torch.allclose(rows, ref[Tc + r * Tl:Tc + (r + 1) * Tl], atol=1e-5)
+        assert torch.allclose(ctx_rows, ref[:Tc], atol=1e-5)
